@@ -5,7 +5,8 @@ from .registry import (ArchitectureEntry, architecture_names, load_config,
 from .qwen3 import Qwen3Config
 from .rusadra import RusadraConfig
 from .pusazen import PusazenConfig
+from .pozelix import PozelixConfig
 
 __all__ = ["ConfigError", "ArchitectureEntry", "architecture_names", "load_config",
            "register_architecture", "resolve_architecture", "unregister_architecture", "Qwen3Config", "RusadraConfig",
-           "PusazenConfig"]
+           "PusazenConfig", "PozelixConfig"]

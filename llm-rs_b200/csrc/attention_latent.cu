@@ -6,7 +6,9 @@
 //
 //   latent_prepare    per token: rotates the rot part of every query head in place and, for a layer that owns its
 //                     cache, norms the latent (x / rms * weight) and rotates the shared key part into the pages.
-//                     Angles are position * base^(-2i/dims), made in double so that they are exact to float32.
+//                     Angles are position * inv_freq[i], made in double so that they are exact to float32; pair i is
+//                     the entries (i, i + dims/2) or, with `neighbours`, (2i, 2i + 1); cosines and sines are
+//                     multiplied by `magnitude` (1 unless the frequencies were rescaled for longer contexts).
 //   latent_attention  one block per (token, group of heads): causal, optionally the last `window` keys only,
 //                     softmax in float32 kept online per warp and merged through shared memory; the result is the
 //                     attention-weighted latent times sigmoid(gate) of the head (the gate is a scalar per head, so it
@@ -21,7 +23,7 @@ __global__ void latent_prepare_kernel(TA* __restrict__ q, long long q_stride, co
                                       const double* __restrict__ inv_freq, const int* __restrict__ positions,
                                       const int* __restrict__ token_req, const int* __restrict__ table,
                                       int table_width, TA* __restrict__ cache, int page_size, int n_heads, int dn,
-                                      int dr, int rot_dims, int rank, float eps) {
+                                      int dr, int rot_dims, int rank, float eps, int neighbours, float magnitude) {
   extern __shared__ float sm[];
   float* cs = sm;                       // [rot_dims / 2] cosines, then as many sines
   float* sn = sm + rot_dims / 2;
@@ -32,17 +34,19 @@ __global__ void latent_prepare_kernel(TA* __restrict__ q, long long q_stride, co
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     double s, c;
     sincos((double)pos * inv_freq[i], &s, &c);
-    cs[i] = (float)c;
-    sn[i] = (float)s;
+    cs[i] = (float)c * magnitude;
+    sn[i] = (float)s * magnitude;
   }
   __syncthreads();
+  // Pair i is the entries (i, i + half), or with `neighbours` the entries (2i, 2i + 1).
+  const int first = neighbours ? 2 : 1, apart = neighbours ? 1 : half;
   TA* qt = q + (size_t)t * q_stride;
   for (int e = threadIdx.x; e < n_heads * half; e += blockDim.x) {
     const int h = e / half, i = e % half;
-    TA* p = qt + (size_t)h * (dn + dr) + dn;
-    const float u = to_float(p[i]), v = to_float(p[i + half]);
-    p[i] = from_float<TA>(u * cs[i] - v * sn[i]);
-    p[i + half] = from_float<TA>(v * cs[i] + u * sn[i]);
+    TA* p = qt + (size_t)h * (dn + dr) + dn + first * i;
+    const float u = to_float(p[0]), v = to_float(p[apart]);
+    p[0] = from_float<TA>(u * cs[i] - v * sn[i]);
+    p[apart] = from_float<TA>(v * cs[i] + u * sn[i]);
   }
   if (dkv == nullptr) return;
   const TA* row = dkv + (size_t)t * dkv_stride;
@@ -63,9 +67,13 @@ __global__ void latent_prepare_kernel(TA* __restrict__ q, long long q_stride, co
   const TA* kr = row + rank;
   for (int i = threadIdx.x; i < dr; i += blockDim.x) {
     float x;
-    if (i < half) x = to_float(kr[i]) * cs[i] - to_float(kr[i + half]) * sn[i];
-    else if (i < rot_dims) x = to_float(kr[i]) * cs[i - half] + to_float(kr[i - half]) * sn[i - half];
-    else x = to_float(kr[i]);
+    if (i >= rot_dims) x = to_float(kr[i]);
+    else if (neighbours) {
+      const int j = i >> 1;
+      x = (i & 1) ? to_float(kr[i]) * cs[j] + to_float(kr[i - 1]) * sn[j]
+                  : to_float(kr[i]) * cs[j] - to_float(kr[i + 1]) * sn[j];
+    } else if (i < half) x = to_float(kr[i]) * cs[i] - to_float(kr[i + half]) * sn[i];
+    else x = to_float(kr[i]) * cs[i - half] + to_float(kr[i - half]) * sn[i - half];
     r_out[i] = from_float<TA>(x);
   }
 }
@@ -74,7 +82,7 @@ LLMRS_API int llmrs_latent_prepare(void* q, long long q_stride, const void* dkv,
                                    const float* latent_norm_w, const double* inv_freq, const int* positions,
                                    const int* token_req, const int* table, int table_width, void* cache,
                                    int page_size, int n_tokens, int n_heads, int dn, int dr, int rot_dims, int rank,
-                                   float eps, cudaStream_t stream) {
+                                   float eps, int neighbours, float magnitude, cudaStream_t stream) {
   LLMRS_REQUIRE(n_tokens >= 0 && n_heads > 0 && dn >= 0 && dr > 0 && rank > 0, "latent_prepare: bad sizes");
   LLMRS_REQUIRE(rot_dims % 2 == 0 && rot_dims >= 0 && rot_dims <= dr, "latent_prepare: %d rotated dimensions of %d",
                 rot_dims, dr);
@@ -84,11 +92,12 @@ LLMRS_API int llmrs_latent_prepare(void* q, long long q_stride, const void* dkv,
   if (dtype == LLMRS_F32)
     latent_prepare_kernel<float><<<n_tokens, 128, smem, stream>>>(
         (float*)q, q_stride, (const float*)dkv, dkv_stride, latent_norm_w, inv_freq, positions, token_req, table,
-        table_width, (float*)cache, page_size, n_heads, dn, dr, rot_dims, rank, eps);
+        table_width, (float*)cache, page_size, n_heads, dn, dr, rot_dims, rank, eps, neighbours, magnitude);
   else if (dtype == LLMRS_BF16)
     latent_prepare_kernel<__nv_bfloat16><<<n_tokens, 128, smem, stream>>>(
         (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)dkv, dkv_stride, latent_norm_w, inv_freq, positions,
-        token_req, table, table_width, (__nv_bfloat16*)cache, page_size, n_heads, dn, dr, rot_dims, rank, eps);
+        token_req, table, table_width, (__nv_bfloat16*)cache, page_size, n_heads, dn, dr, rot_dims, rank, eps,
+        neighbours, magnitude);
   else
     return llmrs_fail("latent_prepare: unknown dtype %d", dtype);
   return llmrs_launch_status("latent_prepare");

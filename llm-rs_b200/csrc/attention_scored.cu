@@ -13,6 +13,9 @@
 //   prepare   RMS norm over the WHOLE q row (all heads at once) and the whole k row with weights of that size
 //             (null: no norm), rotation of the first rot_dims channels of every head (channel i with i + rot_dims/2,
 //             angle position * inv_freq[i], made in double), q rewritten in place, k and v written into their pages;
+//             with `unit_heads` every head of q and k is instead divided by its own root mean square AFTER the
+//             rotation, without a weight;
+//   head gate out[t, h, :] *= sigmoid(gate[t, h]), one number per token and query head;
 //   prefill   16 queries of one request per block against the keys they may see, online softmax (any type);
 //             bfloat16 with dk, dv multiples of 16 up to 128: 64 queries per block on the tensor cores (mma.sync);
 //   decode    one query per request: the visible keys are cut into runs that separate blocks take, and a second
@@ -86,7 +89,7 @@ __global__ void scored_prepare_kernel(T* __restrict__ q, long long q_stride, con
                                       const double* __restrict__ inv_freq, const int* __restrict__ positions,
                                       const int* __restrict__ token_req, const int* __restrict__ block_table,
                                       int table_stride, T* __restrict__ cache, int n_q_heads, int n_kv_heads, int dk,
-                                      int dv, int rot_dims, int page_size, float eps) {
+                                      int dv, int rot_dims, int page_size, float eps, int unit_heads) {
   extern __shared__ float sm[];
   __shared__ float red[33];
   const int t = blockIdx.x, pos = positions[t];
@@ -126,6 +129,33 @@ __global__ void scored_prepare_kernel(T* __restrict__ q, long long q_stride, con
     }
     return a;
   };
+  if (unit_heads) {
+    // Every head of q and k, AFTER its rotation, is divided by its own root mean square (no weight): a warp per head.
+    const int page = k == nullptr ? 0 :
+        LLMRS_CHECKED_PAGE(block_table[(size_t)token_req[t] * table_stride + pos / page_size], 2, t);
+    const int slot = pos % page_size, lane = threadIdx.x & 31;
+    for (int hh = threadIdx.x >> 5; hh < n_q_heads + (k ? n_kv_heads : 0); hh += blockDim.x >> 5) {
+      const bool is_q = hh < n_q_heads;
+      const int head = is_q ? hh : hh - n_q_heads;
+      const float* x = is_q ? xq : xk;
+      float ss = 0.f;
+      for (int i = lane; i < dk; i += 32) {
+        const float a = turned(x, nullptr, 1.0f, head, i);
+        ss = fmaf(a, a, ss);
+      }
+      const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dk + eps);
+      T* dst = is_q ? q + (size_t)t * q_stride + (size_t)head * dk
+                    : cache + page_head_offset(page, head, n_kv_heads, page_size, dk, dv) + (size_t)slot * dk;
+      for (int i = lane; i < dk; i += 32) dst[i] = from_float<T>(turned(x, nullptr, 1.0f, head, i) * inv);
+    }
+    if (k == nullptr) return;
+    for (int c = threadIdx.x; c < n_kv_heads * dv; c += blockDim.x) {
+      const int head = c / dv, i = c % dv;
+      cache[page_head_offset(page, head, n_kv_heads, page_size, dk, dv) + (size_t)page_size * dk + (size_t)slot * dv + i] =
+          v[(size_t)t * v_stride + c];
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < wq; c += blockDim.x)
     q[(size_t)t * q_stride + c] = from_float<T>(turned(xq, q_norm_w, inv_q, c / dk, c % dk));
   if (k == nullptr) return;
@@ -150,7 +180,7 @@ LLMRS_API int llmrs_scored_prepare(void* q, long long q_stride, const void* k, l
                                    const double* inv_freq, const int* positions, const int* token_req,
                                    const int* block_table, int table_stride, void* cache, int n_tokens, int n_q_heads,
                                    int n_kv_heads, int dk, int dv, int rot_dims, int page_size, float eps,
-                                   cudaStream_t stream) {
+                                   int unit_heads, cudaStream_t stream) {
   LLMRS_REQUIRE(n_tokens >= 0 && n_q_heads > 0 && n_kv_heads > 0 && dk > 0 && dv > 0 && page_size > 0,
                 "scored_prepare: bad sizes");
   LLMRS_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dk, "scored_prepare: rot_dims %d of %d", rot_dims, dk);
@@ -169,13 +199,44 @@ LLMRS_API int llmrs_scored_prepare(void* q, long long q_stride, const void* k, l
     }                                                                                                               \
     scored_prepare_kernel<T><<<n_tokens, threads, smem, stream>>>(                                                  \
         (T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, q_norm_w, k_norm_w, inv_freq, positions,     \
-        token_req, block_table, table_stride, (T*)cache, n_q_heads, n_kv_heads, dk, dv, rot_dims, page_size, eps);  \
+        token_req, block_table, table_stride, (T*)cache, n_q_heads, n_kv_heads, dk, dv, rot_dims, page_size, eps,   \
+        unit_heads);                                                                                                \
   } while (0)
   if (dtype == LLMRS_F32) LLMRS_SP_LAUNCH(float);
   else if (dtype == LLMRS_BF16) LLMRS_SP_LAUNCH(__nv_bfloat16);
   else return llmrs_fail("scored_prepare: unknown dtype %d", dtype);
 #undef LLMRS_SP_LAUNCH
   return llmrs_launch_status("scored_prepare");
+}
+
+// ---------------------------------------------------------------------------------
+// head gate: out[t, h, :] *= sigmoid(gate[t, h]) (the sigmoid in float32). One block per token.
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ out, long long out_stride, const T* __restrict__ gate,
+                                 long long gate_stride, int n_heads, int dv) {
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < n_heads * dv; c += blockDim.x) {
+    const float g = 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * gate_stride + c / dv])));
+    T* o = out + (size_t)t * out_stride + c;
+    *o = from_float<T>(to_float(*o) * g);
+  }
+}
+
+LLMRS_API int llmrs_head_gate(void* out, long long out_stride, const void* gate, long long gate_stride, int dtype,
+                              int n_tokens, int n_heads, int dv, cudaStream_t stream) {
+  LLMRS_REQUIRE(n_tokens >= 0 && n_heads > 0 && dv > 0, "head_gate: bad sizes");
+  if (n_tokens == 0) return 0;
+  const int threads = n_heads * dv >= 1024 ? 256 : 128;
+  if (dtype == LLMRS_F32)
+    head_gate_kernel<float><<<n_tokens, threads, 0, stream>>>((float*)out, out_stride, (const float*)gate,
+                                                              gate_stride, n_heads, dv);
+  else if (dtype == LLMRS_BF16)
+    head_gate_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+        (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)gate, gate_stride, n_heads, dv);
+  else
+    return llmrs_fail("head_gate: unknown dtype %d", dtype);
+  return llmrs_launch_status("head_gate");
 }
 
 // ---------------------------------------------------------------------------------

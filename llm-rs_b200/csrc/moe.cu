@@ -46,7 +46,7 @@ constexpr int MOE_SORT_THREADS = 1024, MOE_SORT_WARPS = MOE_SORT_THREADS / 32;
 __global__ void __launch_bounds__(MOE_SORT_THREADS)
 moe_sort_kernel(const int* __restrict__ expert_of, int* __restrict__ row_of, int* __restrict__ src_token,
                 int* __restrict__ tiles, int* __restrict__ n_tiles, int n_assign, int top, int n_experts,
-                int tile_rows) {
+                int tile_rows, int tiled) {
   extern __shared__ int sm[];
   int* counts = sm;                                   // [warps][experts]
   int* start = sm + MOE_SORT_WARPS * n_experts;       // [experts + 1]
@@ -89,7 +89,7 @@ moe_sort_kernel(const int* __restrict__ expert_of, int* __restrict__ row_of, int
     for (int e = 0; e < n_experts; ++e) {
       const int c = start[e + 1];
       tile_at[e] = t;
-      t += (c + tile_rows - 1) / tile_rows;
+      if (e < tiled) t += (c + tile_rows - 1) / tile_rows;      // groups from `tiled` on run no product: no tiles
       rows += c;
       start[e + 1] = rows;
     }
@@ -97,7 +97,7 @@ moe_sort_kernel(const int* __restrict__ expert_of, int* __restrict__ row_of, int
     *n_tiles = t;
   }
   __syncthreads();
-  for (int e = tid; e < n_experts; e += MOE_SORT_THREADS) {
+  for (int e = tid; e < tiled; e += MOE_SORT_THREADS) {
     const int first = start[e], c = start[e + 1] - first;
     for (int i = 0, t = tile_at[e]; i < c; i += tile_rows, ++t) {
       tiles[3 * t] = e;
@@ -113,14 +113,18 @@ moe_sort_kernel(const int* __restrict__ expert_of, int* __restrict__ row_of, int
   }
 }
 
+// `tiled_groups`: only the first so many groups get tiles (the others' rows are sorted but run no product; an identity
+// expert); negative: all.
 LLMRS_API int llmrs_moe_sort(const int* expert_of, int* row_of, int* src_token, int* tiles, int* n_tiles,
-                             int n_assign, int top, int n_experts, int tile_rows, cudaStream_t stream) {
+                             int n_assign, int top, int n_experts, int tile_rows, int tiled_groups,
+                             cudaStream_t stream) {
+  const int tiled = tiled_groups < 0 || tiled_groups > n_experts ? n_experts : tiled_groups;
   LLMRS_REQUIRE(n_assign >= 0 && top > 0 && tile_rows > 0, "moe_sort: bad sizes");
   LLMRS_REQUIRE(n_experts > 0 && n_experts <= 256, "moe_sort: 1 to 256 experts, got %d", n_experts);
   if (n_assign == 0) return 0;
   const size_t smem = ((size_t)MOE_SORT_WARPS * n_experts + 2 * (n_experts + 1)) * sizeof(int);
   moe_sort_kernel<<<1, MOE_SORT_THREADS, smem, stream>>>(expert_of, row_of, src_token, tiles, n_tiles, n_assign, top,
-                                                         n_experts, tile_rows);
+                                                         n_experts, tile_rows, tiled);
   return llmrs_launch_status("moe_sort");
 }
 
@@ -249,4 +253,114 @@ LLMRS_API int llmrs_moe_combine_shared(const float* rows, const int* row_of, con
   else
     return llmrs_fail("moe_combine_shared: unknown dtype %d", shared_dtype);
   return llmrs_launch_status("moe_combine_shared");
+}
+
+// ---------------------------------------------------------------------------------
+// Router "softmax_bias": scores s = softmax(logits) over ALL experts; the `top` experts with the largest s + bias are
+// chosen (among equals the lower expert), and their weights are the scores s themselves, not renormalised. The last
+// experts (from `n_real` on) are identity experts: they have no weights of their own and are all reported as group
+// `n_real`, whose rows run no product. One warp per token, assignments in order of falling choice score.
+// ---------------------------------------------------------------------------------
+__global__ void moe_route_biased_kernel(const float* __restrict__ logits, long long stride,
+                                        const float* __restrict__ bias, int* __restrict__ expert_of,
+                                        float* __restrict__ weight_of, int n_tokens, int n_all, int n_real, int top) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= n_tokens) return;
+  float s[ROUTE_PER_LANE], c[ROUTE_PER_LANE];
+  float m = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < ROUTE_PER_LANE; ++j) {
+    const int e = lane + 32 * j;
+    s[j] = e < n_all ? logits[(size_t)t * stride + e] : -INFINITY;
+    m = fmaxf(m, s[j]);
+  }
+  m = warp_max(m);
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < ROUTE_PER_LANE; ++j) {
+    s[j] = lane + 32 * j < n_all ? expf(s[j] - m) : 0.f;
+    sum += s[j];
+  }
+  sum = warp_sum(sum);
+#pragma unroll
+  for (int j = 0; j < ROUTE_PER_LANE; ++j) {
+    const int e = lane + 32 * j;
+    s[j] = s[j] / sum;
+    c[j] = e < n_all ? s[j] + (bias ? bias[e] : 0.f) : -INFINITY;
+  }
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY, score = 0.f;
+    int at = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < ROUTE_PER_LANE; ++j) {
+      const int e = lane + 32 * j;
+      if (e < n_all && c[j] != -INFINITY && (c[j] > best || (c[j] == best && e < at))) { best = c[j]; at = e; score = s[j]; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      const float os = __shfl_xor_sync(0xffffffffu, score, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; score = os; }
+    }
+    if (at == 0x7fffffff) { at = k; score = 0.f; }      // logits that are no numbers: any expert, weight 0
+#pragma unroll
+    for (int j = 0; j < ROUTE_PER_LANE; ++j)
+      if (lane + 32 * j == at) c[j] = -INFINITY;
+    if (lane == 0) {
+      expert_of[(size_t)t * top + k] = at < n_real ? at : n_real;
+      weight_of[(size_t)t * top + k] = score;
+    }
+  }
+}
+
+LLMRS_API int llmrs_moe_route_biased(const float* logits, long long stride, const float* bias, int* expert_of,
+                                     float* weight_of, int n_tokens, int n_all, int n_real, int top,
+                                     cudaStream_t stream) {
+  LLMRS_REQUIRE(n_tokens >= 0 && top > 0 && top <= n_all && n_real >= 0 && n_real <= n_all,
+                "moe_route_biased: bad sizes");
+  LLMRS_REQUIRE(n_all <= 32 * ROUTE_PER_LANE, "moe_route_biased: at most %d experts, got %d", 32 * ROUTE_PER_LANE,
+                n_all);
+  if (n_tokens == 0) return 0;
+  moe_route_biased_kernel<<<(n_tokens + 3) / 4, 128, 0, stream>>>(logits, stride, bias, expert_of, weight_of,
+                                                                 n_tokens, n_all, n_real, top);
+  return llmrs_launch_status("moe_route_biased");
+}
+
+// ---------------------------------------------------------------------------------
+// moe_combine where an assignment to group `n_real` (an identity expert) stands for the token's own input row:
+// out[t, :] = sum_k weight_of[t, k] * (expert_of[t, k] < n_real ? rows[row_of[t, k], :] : x[t, :]), k in order.
+// ---------------------------------------------------------------------------------
+template <typename TX>
+__global__ void moe_combine_identity_kernel(const float* __restrict__ rows, const int* __restrict__ row_of,
+                                            const float* __restrict__ weight_of, const int* __restrict__ expert_of,
+                                            const TX* __restrict__ x, float* __restrict__ out, int top, int width,
+                                            int n_real) {
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float s = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int a = t * top + k;
+      const float v = expert_of[a] < n_real ? rows[(size_t)row_of[a] * width + c] : to_float(x[(size_t)t * width + c]);
+      s = fmaf(weight_of[a], v, s);
+    }
+    out[(size_t)t * width + c] = s;
+  }
+}
+
+LLMRS_API int llmrs_moe_combine_identity(const float* rows, const int* row_of, const float* weight_of,
+                                         const int* expert_of, const void* x, int x_dtype, float* out, int n_tokens,
+                                         int top, int width, int n_real, cudaStream_t stream) {
+  LLMRS_REQUIRE(n_tokens >= 0 && top > 0 && width > 0, "moe_combine_identity: bad sizes");
+  if (n_tokens == 0) return 0;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (x_dtype == LLMRS_F32)
+    moe_combine_identity_kernel<float><<<n_tokens, threads, 0, stream>>>(rows, row_of, weight_of, expert_of,
+                                                                         (const float*)x, out, top, width, n_real);
+  else if (x_dtype == LLMRS_BF16)
+    moe_combine_identity_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+        rows, row_of, weight_of, expert_of, (const __nv_bfloat16*)x, out, top, width, n_real);
+  else
+    return llmrs_fail("moe_combine_identity: unknown dtype %d", x_dtype);
+  return llmrs_launch_status("moe_combine_identity");
 }

@@ -140,3 +140,88 @@ LLMRS_API int llmrs_tanh_slice(const void* in, int in_dtype, long long in_stride
     return llmrs_fail("tanh_slice: unsupported types %d -> %d", in_dtype, out_dtype);
   return llmrs_launch_status("tanh_slice");
 }
+
+// ---------------------------------------------------------------------------------
+// The two norms between the branches of a block that norms a branch before AND after it, in one pass over a row:
+//   h[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w_out            (the norm on the branch's output and the residual sum)
+//   out[t] = h[t] / sqrt(mean(h[t]^2) + eps) * w_next          (the norm ahead of the next branch; w_next null: none)
+// One block per row; the row's new values wait in shared memory for their statistics.
+// ---------------------------------------------------------------------------------
+template <typename TY, typename TO>
+__global__ void outnorm_add_norm_kernel(float* __restrict__ h, const TY* __restrict__ y,
+                                        const float* __restrict__ w_out, const float* __restrict__ w_next,
+                                        TO* __restrict__ out, int width, float eps) {
+  extern __shared__ float row[];
+  __shared__ float red[33];
+  const TY* yr = y + (size_t)blockIdx.x * width;
+  float* hr = h + (size_t)blockIdx.x * width;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = to_float(yr[c]);
+    ss += v * v;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
+  ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = hr[c] + to_float(yr[c]) * inv * w_out[c];
+    hr[c] = v;
+    row[c] = v;
+    ss += v * v;
+  }
+  const float inv2 = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
+  TO* o = out + (size_t)blockIdx.x * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) o[c] = from_float<TO>(row[c] * inv2 * w_next[c]);
+}
+
+LLMRS_API int llmrs_outnorm_add_norm(float* h, const void* y, int y_dtype, const float* w_out, const float* w_next,
+                                     void* out, int out_dtype, int n_rows, int width, float eps,
+                                     cudaStream_t stream) {
+  LLMRS_REQUIRE(n_rows >= 0 && width > 0 && width <= 12288, "outnorm_add_norm: rows of 1 to 12288, got %d", width);
+  LLMRS_REQUIRE(w_next != nullptr && out != nullptr, "outnorm_add_norm: the second norm needs its weight and output");
+  if (n_rows == 0) return 0;
+  const int threads = width >= 1024 ? 256 : 128;
+  const size_t smem = (size_t)width * sizeof(float);
+#define LLMRS_OAN(TY, TO)                                                                                       \
+  outnorm_add_norm_kernel<TY, TO><<<n_rows, threads, smem, stream>>>(h, (const TY*)y, w_out, w_next, (TO*)out, \
+                                                                     width, eps)
+  if (y_dtype == LLMRS_F32 && out_dtype == LLMRS_F32) LLMRS_OAN(float, float);
+  else if (y_dtype == LLMRS_BF16 && out_dtype == LLMRS_BF16) LLMRS_OAN(__nv_bfloat16, __nv_bfloat16);
+  else if (y_dtype == LLMRS_F32 && out_dtype == LLMRS_BF16) LLMRS_OAN(float, __nv_bfloat16);
+  else return llmrs_fail("outnorm_add_norm: unsupported types %d -> %d", y_dtype, out_dtype);
+#undef LLMRS_OAN
+  return llmrs_launch_status("outnorm_add_norm");
+}
+
+// ---------------------------------------------------------------------------------
+// out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w for rows of activations (a column slice of a wider product: x has a
+// row stride), statistics in float32. One block per row.
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void rmsnorm_rows_kernel(const T* __restrict__ x, long long x_stride, const float* __restrict__ w,
+                                    T* __restrict__ out, int width, float eps) {
+  __shared__ float red[33];
+  const T* xr = x + (size_t)blockIdx.x * x_stride;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = to_float(xr[c]);
+    ss += v * v;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
+  T* o = out + (size_t)blockIdx.x * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) o[c] = from_float<T>(to_float(xr[c]) * inv * w[c]);
+}
+
+LLMRS_API int llmrs_rmsnorm_rows(const void* x, long long x_stride, int dtype, const float* w, void* out, int n_rows,
+                                 int width, float eps, cudaStream_t stream) {
+  LLMRS_REQUIRE(n_rows >= 0 && width > 0 && x_stride >= width, "rmsnorm_rows: bad sizes");
+  if (n_rows == 0) return 0;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (dtype == LLMRS_F32)
+    rmsnorm_rows_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)x, x_stride, w, (float*)out, width, eps);
+  else if (dtype == LLMRS_BF16)
+    rmsnorm_rows_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>((const __nv_bfloat16*)x, x_stride, w,
+                                                                       (__nv_bfloat16*)out, width, eps);
+  else
+    return llmrs_fail("rmsnorm_rows: unknown dtype %d", dtype);
+  return llmrs_launch_status("rmsnorm_rows");
+}

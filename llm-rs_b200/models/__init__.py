@@ -1,5 +1,5 @@
 """Architectures: each module turns its typed configuration into a ``ModelSpec`` and
 registers itself by the name found in config.json."""
-from . import pusazen, qwen3, rusadra
+from . import pozelix, pusazen, qwen3, rusadra
 
-__all__ = ["pusazen", "qwen3", "rusadra"]
+__all__ = ["pozelix", "pusazen", "qwen3", "rusadra"]

@@ -830,9 +830,11 @@ def moe_route_table(token_ids: torch.Tensor, table: torch.Tensor, n_experts: int
     return expert_of, weight_of
 
 
-def moe_sort(expert_of: torch.Tensor, top: int, n_experts: int, tile_rows: int = GROUPED_TILE_ROWS):
+def moe_sort(expert_of: torch.Tensor, top: int, n_experts: int, tile_rows: int = GROUPED_TILE_ROWS,
+             tiled_groups: int = -1):
     """Order the assignments by expert. Returns (row_of [assignments], src_token [assignments], tiles [max, 3],
-    n_tiles [1]): see ``gemm_grouped``."""
+    n_tiles [1]): see ``gemm_grouped``. With ``tiled_groups`` >= 0 only the first so many groups get tiles: the rows
+    of the others are sorted but run no product."""
     _need(expert_of, "expert_of", torch.int32)
     n = expert_of.numel()
     dev = expert_of.device
@@ -842,7 +844,7 @@ def moe_sort(expert_of: torch.Tensor, top: int, n_experts: int, tile_rows: int =
     tiles = torch.empty((max_tiles, 3), dtype=torch.int32, device=dev)
     n_tiles = torch.empty((1,), dtype=torch.int32, device=dev)
     _check(_lib().llmrs_moe_sort(_ptr(expert_of), _ptr(row_of), _ptr(src_token), _ptr(tiles), _ptr(n_tiles), n, top,
-                                 n_experts, tile_rows, _stream()), "moe_sort")
+                                 n_experts, tile_rows, tiled_groups, _stream()), "moe_sort")
     return row_of, src_token, tiles, n_tiles
 
 
@@ -883,10 +885,11 @@ def delta_rule(r, k, v, gate, a_raw, decay_raw, decay_bias, a_bias, norm_w, stat
 # -- latent attention -----------------------------------------------------------------------------------
 def latent_prepare(q: torch.Tensor, dkv: Optional[torch.Tensor], latent_norm_w, inv_freq: torch.Tensor, ctx, table,
                    cache: Optional[torch.Tensor], page_size: int, n_heads: int, dn: int, dr: int, rot_dims: int,
-                   rank: int, eps: float) -> None:
+                   rank: int, eps: float, neighbours: bool = False, magnitude: float = 1.0) -> None:
     """Rotate the rot part of every query head of ``q`` ([tokens, heads * (dn + dr)] view) in place; with ``dkv``
     ([tokens, rank + dr] view) also norm the latent and rotate the shared key part into the pages ``cache``
-    ([pages, 1, page_size * (rank + dr)])."""
+    ([pages, 1, page_size * (rank + dr)]). Pair i of the rotation is the entries (i, i + rot_dims/2), with
+    ``neighbours`` (2i, 2i + 1); cosines and sines are multiplied by ``magnitude``."""
     _need(q, "q", contiguous=False)
     _need(inv_freq, "inv_freq", torch.float64)
     if dkv is not None:
@@ -896,7 +899,8 @@ def latent_prepare(q: torch.Tensor, dkv: Optional[torch.Tensor], latent_norm_w, 
         _ptr(q), _LL(_row_stride(q, "q")), _ptr(dkv), _LL(0 if dkv is None else _row_stride(dkv, "dkv")),
         dtype_code(q.dtype), _ptr(latent_norm_w), _ptr(inv_freq), _ptr(ctx.positions), _ptr(ctx.token_req),
         _ptr(table), 0 if table is None else table.size(1), _ptr(cache), page_size, q.size(0), n_heads, dn, dr,
-        rot_dims, rank, ctypes.c_float(eps), _stream()), "latent_prepare")
+        rot_dims, rank, ctypes.c_float(eps), int(bool(neighbours)), ctypes.c_float(magnitude), _stream()),
+        "latent_prepare")
 
 
 LATENT_FEW_TOKENS = 64      # steps of at most this many tokens take the latent attention kernel laid out for latency
@@ -1073,9 +1077,11 @@ MASK_CAUSAL, MASK_WINDOW, MASK_CHUNK = 0, 1, 2
 
 def scored_prepare(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], q_norm_w, k_norm_w,
                    inv_freq: torch.Tensor, ctx, table, cache: Optional[torch.Tensor], n_q_heads: int,
-                   n_kv_heads: int, dk: int, dv: int, rot_dims: int, page_size: int, eps: float) -> None:
+                   n_kv_heads: int, dk: int, dv: int, rot_dims: int, page_size: int, eps: float,
+                   unit_heads: bool = False) -> None:
     """Norm over the whole q and k rows, rotation, q rewritten in place, k and v into the pages ``cache``
-    ([pages, kv heads, page_size * (dk + dv)]); see ``csrc/attention_scored.cu``."""
+    ([pages, kv heads, page_size * (dk + dv)]); with ``unit_heads`` every head of q and k is instead divided by its
+    own root mean square after the rotation (no weights); see ``csrc/attention_scored.cu``."""
     _need(q, "q", contiguous=False)
     _need(inv_freq, "inv_freq", torch.float64)
     if k is not None:
@@ -1086,8 +1092,8 @@ def scored_prepare(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch
         _ptr(q), _LL(_row_stride(q, "q")), _ptr(k), _LL(0 if k is None else _row_stride(k, "k")), _ptr(v),
         _LL(0 if v is None else _row_stride(v, "v")), dtype_code(q.dtype), _ptr(q_norm_w), _ptr(k_norm_w),
         _ptr(inv_freq), _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(table), 0 if table is None else table.size(1),
-        _ptr(cache), q.size(0), n_q_heads, n_kv_heads, dk, dv, rot_dims, page_size, ctypes.c_float(eps), _stream()),
-        "scored_prepare")
+        _ptr(cache), q.size(0), n_q_heads, n_kv_heads, dk, dv, rot_dims, page_size, ctypes.c_float(eps),
+        int(bool(unit_heads)), _stream()), "scored_prepare")
 
 
 def scored_generic_only(on: bool) -> None:
@@ -1169,4 +1175,87 @@ def moe_combine_shared(rows, row_of, weight_of, top: int, shared: Optional[torch
     _check(_lib().llmrs_moe_combine_shared(
         _ptr(rows), _ptr(row_of), _ptr(weight_of), _ptr(shared), dtype_code(shared.dtype) if shared is not None else F32,
         _ptr(shared_gate), _LL(gate_stride), _ptr(out), n, top, rows.size(1), _stream()), "moe_combine_shared")
+    return out
+
+
+def head_gate(out: torch.Tensor, gate: torch.Tensor, n_heads: int, dv: int) -> torch.Tensor:
+    """``out[t, h, :] *= sigmoid(gate[t, h])`` in place: ``out`` [tokens, heads * dv], ``gate`` [tokens, heads] (views
+    with dense rows, the same type)."""
+    _need(out, "out", contiguous=False)
+    _need(gate, "gate", out.dtype, contiguous=False)
+    if out.size(1) != n_heads * dv or gate.size(1) != n_heads or gate.size(0) != out.size(0):
+        raise KernelError(f"head_gate: out {tuple(out.shape)}, gate {tuple(gate.shape)}, {n_heads} heads of {dv}")
+    _check(_lib().llmrs_head_gate(_ptr(out), _LL(_row_stride(out, "out")), _ptr(gate), _LL(_row_stride(gate, "gate")),
+                                  dtype_code(out.dtype), out.size(0), n_heads, dv, _stream()), "head_gate")
+    return out
+
+
+# -- a router that scores all experts, and experts that return their input ---------------------------------
+def moe_route_biased(logits: torch.Tensor, bias: Optional[torch.Tensor], n_all: int, n_real: int, top: int):
+    """Scores ``s = softmax(logits[:, :n_all])``; the ``top`` experts with the largest ``s + bias`` are chosen (the
+    lower expert among equals) and weighted by ``s`` itself. Experts from ``n_real`` on are identity experts and are
+    all reported as group ``n_real``. Returns (expert_of int32 [tokens * top], weight_of float32 [tokens * top]) in
+    order of falling choice score."""
+    _need(logits, "logits", torch.float32, contiguous=False)
+    n = logits.size(0)
+    if logits.size(1) < n_all or not 1 <= top <= n_all or not 0 <= n_real <= n_all:
+        raise KernelError(f"moe_route_biased: logits {tuple(logits.shape)}, {n_all} experts ({n_real} real), top {top}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != n_all:
+            raise KernelError(f"moe_route_biased: {bias.numel()} corrections for {n_all} experts")
+    expert_of = torch.empty((n * top,), dtype=torch.int32, device=logits.device)
+    weight_of = torch.empty((n * top,), dtype=torch.float32, device=logits.device)
+    _check(_lib().llmrs_moe_route_biased(_ptr(logits), _LL(_row_stride(logits, "logits")), _ptr(bias), _ptr(expert_of),
+                                         _ptr(weight_of), n, n_all, n_real, top, _stream()), "moe_route_biased")
+    return expert_of, weight_of
+
+
+def moe_combine_identity(rows: torch.Tensor, row_of: torch.Tensor, weight_of: torch.Tensor, expert_of: torch.Tensor,
+                         x: torch.Tensor, top: int, n_real: int) -> torch.Tensor:
+    """``moe_combine`` in which an assignment to group ``n_real`` stands for the token's own input row ``x[t]``."""
+    _need(rows, "rows", torch.float32)
+    _need(x, "x")
+    n = row_of.numel() // top
+    if x.size(0) != n or x.size(1) != rows.size(1):
+        raise KernelError(f"moe_combine_identity: x {tuple(x.shape)}, rows of {rows.size(1)}, {n} tokens")
+    out = torch.empty((n, rows.size(1)), dtype=torch.float32, device=rows.device)
+    _check(_lib().llmrs_moe_combine_identity(_ptr(rows), _ptr(row_of), _ptr(weight_of), _ptr(expert_of), _ptr(x),
+                                             dtype_code(x.dtype), _ptr(out), n, top, rows.size(1), n_real, _stream()),
+           "moe_combine_identity")
+    return out
+
+
+# -- norms of a block that norms a branch before and after it ------------------------------------------------
+def outnorm_add_norm(h: torch.Tensor, y: torch.Tensor, w_out: torch.Tensor, w_next: torch.Tensor, eps: float,
+                     out_dtype: torch.dtype) -> torch.Tensor:
+    """``h += y / rms(y) * w_out`` in place (float32), and in the same pass ``h / rms(h) * w_next`` of the new rows,
+    returned in ``out_dtype``: the norm on a branch's output, the residual sum and the norm ahead of the next branch."""
+    _need(h, "h", torch.float32)
+    _need(y, "y")
+    _need(w_out, "w_out", torch.float32)
+    _need(w_next, "w_next", torch.float32)
+    if y.shape != h.shape or w_out.numel() != h.size(-1) or w_next.numel() != h.size(-1):
+        raise KernelError(f"outnorm_add_norm: h {tuple(h.shape)}, y {tuple(y.shape)}, weights {w_out.numel()}, "
+                          f"{w_next.numel()}")
+    out = torch.empty(tuple(h.shape), dtype=out_dtype, device=h.device)
+    _check(_lib().llmrs_outnorm_add_norm(_ptr(h), _ptr(y), dtype_code(y.dtype), _ptr(w_out), _ptr(w_next), _ptr(out),
+                                         dtype_code(out_dtype), h.size(0), h.size(1), ctypes.c_float(eps), _stream()),
+           "outnorm_add_norm")
+    return out
+
+
+OUTNORM_ADD_NORM_MAX_WIDTH = 12288
+
+
+def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """``x / sqrt(mean(x^2) + eps) * weight`` for rows of activations (a view with dense rows), float32 statistics;
+    returns a contiguous tensor of the same type."""
+    _need(x, "x", contiguous=False)
+    _need(weight, "weight", torch.float32)
+    if weight.numel() != x.size(1):
+        raise KernelError(f"rmsnorm_rows: rows of {x.size(1)}, weight {weight.numel()}")
+    out = torch.empty(tuple(x.shape), dtype=x.dtype, device=x.device)
+    _check(_lib().llmrs_rmsnorm_rows(_ptr(x), _LL(_row_stride(x, "x")), dtype_code(x.dtype), _ptr(weight), _ptr(out),
+                                     x.size(0), x.size(1), ctypes.c_float(eps), _stream()), "rmsnorm_rows")
     return out

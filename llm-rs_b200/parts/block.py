@@ -8,12 +8,14 @@ import torch
 from .. import ops
 from .base import Block, Part, PreNormed, Runtime
 from .registry import build, register
-from .spec import LayerSpec, StateNeed, WeightSpec
+from .spec import LayerSpec, PartSpec, StateNeed, WeightSpec
 
 
 # Steps of few tokens spread each norm over the products around it (see ``PreNormed``); LLMRS_LINK_NORMS=0
 # keeps the norm kernels.
 LINK_NORMS = os.environ.get("LLMRS_LINK_NORMS", "1") != "0"
+# LLMRS_FUSE_SANDWICH=0: a block with norms on both sides of a branch runs every norm as a kernel of its own.
+FUSE_SANDWICH = os.environ.get("LLMRS_FUSE_SANDWICH", "1") != "0"
 
 
 @register("block", "prenorm")
@@ -196,4 +198,58 @@ class PostNormBlock(Block):
             y = self.feed_forward.forward(x, ctx) if self.feed_forward is not None else None
             x = self.feed_forward_norm.post_normed(h, y, self.scales[1], self.alpha, self.act_dtype)
         ctx.stream_copy = (h, x)
+        return h, None
+
+
+@register("block", "sandwich")
+class SandwichBlock(Block):
+    """``h += norm_b(mixer(norm_a(h))); h += norm_d(feed_forward(norm_c(h)))``: a norm ahead of every branch AND one on
+    its output. ``layer.mixer_norm`` and ``layer.feed_forward_norm`` are the norms ahead of the branches; ``out_norms``
+    names the weights of the two output norms after the layer's prefix (same size and eps). A layer may have no
+    feed-forward. The norm on the mixer's output, the residual sum and the norm ahead of the feed-forward are one pass
+    over the rows (``ops.outnorm_add_norm``). Sums and statistics are float32."""
+
+    def __init__(self, layer: LayerSpec, out_norms=("norm1b", "norm2b"), prefix: str = ""):
+        p = layer.prefix
+        self.mixer_norm = build("norm", layer.mixer_norm, prefix=p)
+        self.mixer = build("mixer", layer.mixer, prefix=p + layer.mixer_scope)
+        dim, eps = self.mixer_norm.dim, self.mixer_norm.eps
+        out_spec = lambda name: PartSpec("rmsnorm", {"dim": dim, "eps": eps, "name": name})
+        self.mixer_out_norm = build("norm", out_spec(out_norms[0]), prefix=p)
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_out_norm = None
+        if layer.feed_forward is not None:
+            self.feed_forward_norm = build("norm", layer.feed_forward_norm, prefix=p)
+            self.feed_forward = build("feed_forward", layer.feed_forward, prefix=p + layer.feed_forward_scope)
+            self.feed_forward_out_norm = build("norm", out_spec(out_norms[1]), prefix=p)
+        self.dim = dim
+
+    def parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.mixer_out_norm, self.feed_forward_norm,
+                            self.feed_forward, self.feed_forward_out_norm) if p is not None]
+
+    def chain(self):
+        return []
+
+    def weight_specs(self):
+        return [s for part in self.parts() for s in part.weight_specs()]
+
+    def bind(self, tensors, runtime: Runtime):
+        self.act_dtype = runtime.act_dtype
+        for part in self.parts():
+            part.bind(tensors, runtime)
+
+    def forward(self, h, pending, ctx, cache):
+        x = self.mixer_norm.forward(h, pending)
+        y = self.mixer.forward(x, ctx, cache)
+        if self.feed_forward is None:
+            self.mixer_out_norm.add_normed(h, y)
+            return h, None
+        nxt = self.feed_forward_norm
+        if (FUSE_SANDWICH and self.dim <= ops.OUTNORM_ADD_NORM_MAX_WIDTH and nxt.eps == self.mixer_out_norm.eps
+                and (y.dtype == self.act_dtype or y.dtype == torch.float32)):
+            x = ops.outnorm_add_norm(h, y, self.mixer_out_norm.weight, nxt.weight, nxt.eps, self.act_dtype)
+        else:
+            self.mixer_out_norm.add_normed(h, y)
+            x = nxt.forward(h, None)
+        self.feed_forward_out_norm.add_normed(h, self.feed_forward.forward(x, ctx))
         return h, None

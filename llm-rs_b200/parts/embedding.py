@@ -59,3 +59,42 @@ class LinearHead(Part):
         if self.scale != 1.0:
             ops.scale_(logits, self.scale)
         return ops.softcap_(logits, self.softcap) if self.softcap > 0 else logits
+
+
+@register("reentry", "embedding_mix")
+class EmbeddingMix(Part):
+    """``h <- W [h ; h0]`` with ``W`` of shape [hidden, 2 hidden] (the stream's half first) and ``h0`` the embedding
+    output: what a looped stretch of layers does to the stream ahead of every pass. The product is split into its two
+    halves, ``W_a h + W_b h0``; the second term is the same in every pass of a step and is made once (``prepare``).
+    The rows enter the products in the activation type; the sum and the new stream are float32."""
+
+    def __init__(self, hidden_size: int, name: str = "loop.in", prefix: str = ""):
+        self.hidden_size, self.name = hidden_size, prefix + name
+
+    def weight_specs(self):
+        return [WeightSpec(self.name, (self.hidden_size, 2 * self.hidden_size))]
+
+    def bind(self, tensors, runtime: Runtime):
+        w, D = tensors[self.name], self.hidden_size
+        self.act_dtype = runtime.act_dtype
+        self.of_stream = Linear(w[:, :D].contiguous(), None, runtime.act_dtype)
+        self.of_embedding = Linear(w[:, D:].contiguous(), None, runtime.act_dtype)
+        self.of_stream.warms_next = self.of_embedding.warms_next = False
+
+    def prepare(self, h0, ctx):
+        """``W_b h0`` in float32 for the step's tokens."""
+        return self.of_embedding.forward(ops.token_shift(h0, None, None, ctx, self.act_dtype), out_dtype=torch.float32)
+
+    def forward(self, h, pending, entered, ctx):
+        """The new stream (a tensor of its own: ``h`` and ``entered`` stay as they are). ``pending`` is a branch output
+        that the block before has not added yet."""
+        if pending is not None:
+            ops.residual_add(h, pending)
+        ctx.stream_copy = None
+        new = entered.clone()
+        x = ops.token_shift(h, None, None, ctx, self.act_dtype)
+        if x.dtype == torch.bfloat16 and self.of_stream.uses_tc(x.size(0)):
+            ops.gemm_bf16(x, self.of_stream.weight, out=new, epilogue="residual")      # new += W_a x in the epilogue
+        else:
+            ops.residual_add(new, self.of_stream.forward(x, out_dtype=torch.float32))
+        return new

@@ -1,8 +1,9 @@
 """Latent attention: all heads share one cached row per token."""
 from __future__ import annotations
 
+import math
 import os
-from typing import Optional
+from typing import Mapping, Optional
 
 import numpy as np
 import torch
@@ -18,6 +19,28 @@ from .spec import CacheNeed, WeightSpec
 # CUDA-core kernel for everything.
 _LATENT_MMA = os.environ.get("LLMRS_LATENT_MMA", "1") != "0"
 PREFILL_MIN_TOKENS = 32
+
+
+def rescaled_frequencies(dims: int, base: float, scaling: Optional[Mapping] = None):
+    """(inverse frequencies float64 [dims/2], magnitude) of a rotation of ``dims`` entries: ``f_i = base^(-2i/dims)``.
+
+    ``scaling`` (factor, original, fast, slow) stretches the slow pairs for contexts longer than the ``original`` one
+    (YaRN: Peng, Quesnelle, Fan, Shippole, "YaRN: Efficient Context Window Extension of Large Language Models"). A
+    pair that turns ``t`` times within the original context has index ``d(t) = dims * ln(original / (2 pi t)) / (2 ln
+    base)``; pairs below ``lo = max(floor(d(fast)), 0)`` keep their frequency, pairs above ``hi = min(ceil(d(slow)),
+    dims - 1)`` have it divided by ``factor``, and between them the two are blended by ``ramp_i = clamp((i - lo) /
+    max(hi - lo, 0.001), 0, 1)``: ``f_i / factor * ramp_i + f_i * (1 - ramp_i)``. Cosines and sines are multiplied by
+    the magnitude ``0.1 ln(factor) + 1``."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = float(base) ** (-2.0 * i / max(dims, 1))
+    if not scaling:
+        return f, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+    index = lambda turns: dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))
+    lo = max(math.floor(index(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(index(float(scaling["slow"]))), dims - 1)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
 
 
 def portion_tiles(q_start, n_new, tile_tokens: int) -> np.ndarray:
@@ -47,25 +70,34 @@ class LatentAttention(Mixer):
     Computed in the folded form: ``qa_h = W_uk,h^T q_n,h`` (a batched product), attention over the cached rows with
     values c, then ``W_uv,h`` on the result (a batched product): the cache is read once for all heads and no key or
     value is ever materialised. The rotation pairs entry i of the rotated part with entry i + rot_dims/2 for the first
-    ``rot_dims`` entries, angle ``position * rot_base^(-2i/rot_dims)``.
+    ``rot_dims`` entries (``rot_pairing`` "half"), or entry 2i with 2i + 1 ("neighbours"), angle ``position *
+    rot_base^(-2i/rot_dims)``; ``rot_scaling`` rescales the frequencies (``rescaled_frequencies``).
+
+    ``q_rank`` > 0: the queries go through a latent of their own, ``q = W_uq rmsnorm(W_dq x)`` with a plain norm
+    weight; the down-projection shares the product of the gates and the key/value down-projection.
 
     A layer with ``shares_cache`` has no down-projection: its run-order entry reads another entry's pages
     (``RunStep.cache_of``) with its own up-projections, queries and window. ``cache_window`` is the window the pages
     are kept for (the widest window of the layers that read them; default: this layer's).
 
-    ``names`` maps the roles q, dkv, dkv_norm, uk, uv, g, o to tensor names after the prefix.
+    ``names`` maps the roles q, dq, dq_norm, uq, dkv, dkv_norm, uk, uv, g, o to tensor names after the prefix.
     """
-    ROLES = ("q", "dkv", "dkv_norm", "uk", "uv", "g", "o")
+    ROLES = ("q", "dq", "dq_norm", "uq", "dkv", "dkv_norm", "uk", "uv", "g", "o")
+    PAIRINGS = ("half", "neighbours")
 
     def __init__(self, hidden_size: int, n_heads: int, dim: int, rot_dim: int, vdim: int, rank: int, scale: float,
                  rot_base: float, rot_dims: Optional[int] = None, window: int = 0, cache_window: Optional[int] = None,
-                 norm_eps: float = 1e-6, gated: bool = True, shares_cache: bool = False, names=None,
-                 prefix: str = ""):
+                 norm_eps: float = 1e-6, gated: bool = True, shares_cache: bool = False, q_rank: int = 0,
+                 rot_pairing: str = "half", rot_scaling: Optional[Mapping] = None, names=None, prefix: str = ""):
         self.hidden_size, self.n_heads, self.dim, self.rot_dim, self.vdim = hidden_size, n_heads, dim, rot_dim, vdim
         self.rank, self.scale, self.rot_base = rank, float(scale), float(rot_base)
         self.rot_dims = rot_dim if rot_dims is None else int(rot_dims)
         if self.rot_dims % 2 or not 0 <= self.rot_dims <= rot_dim:
             raise ValueError(f"{self.rot_dims} rotated dimensions of a rotated part of {rot_dim}")
+        if rot_pairing not in self.PAIRINGS:
+            raise ValueError(f"unknown rot_pairing {rot_pairing!r}; known: {self.PAIRINGS}")
+        self.q_rank, self.rot_pairing = int(q_rank), rot_pairing
+        self.rot_scaling = dict(rot_scaling) if rot_scaling else None
         if rank > 512:
             raise ValueError(f"a latent of {rank}: the attention kernel takes at most 512")
         self.window = int(window)
@@ -75,7 +107,8 @@ class LatentAttention(Mixer):
                              f"{self.window or 'all'} keys")
         self.norm_eps, self.gated, self.shares_cache = float(norm_eps), bool(gated), bool(shares_cache)
         self.prefix = prefix
-        self.names = {"q": "q", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "g": "g", "o": "o"}
+        self.names = {"q": "q", "dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm",
+                      "uk": "uk", "uv": "uv", "g": "g", "o": "o"}
         self.names.update(names or {})
         if set(self.names) != set(self.ROLES):
             raise ValueError(f"names may rename {self.ROLES}, got {sorted(set(self.names) - set(self.ROLES))}")
@@ -87,8 +120,13 @@ class LatentAttention(Mixer):
 
     def weight_specs(self):
         H, nh, nm = self.hidden_size, self.n_heads, self._name
-        specs = [WeightSpec(nm("q"), (self.q_width, H)), WeightSpec(nm("uk"), (nh * self.dim, self.rank)),
+        specs = [WeightSpec(nm("uk"), (nh * self.dim, self.rank)),
                  WeightSpec(nm("uv"), (nh * self.vdim, self.rank)), WeightSpec(nm("o"), (H, nh * self.vdim))]
+        if self.q_rank:
+            specs += [WeightSpec(nm("dq"), (self.q_rank, H)), WeightSpec(nm("dq_norm"), (self.q_rank,), role="norm"),
+                      WeightSpec(nm("uq"), (self.q_width, self.q_rank))]
+        else:
+            specs.append(WeightSpec(nm("q"), (self.q_width, H)))
         if self.gated:
             specs.append(WeightSpec(nm("g"), (nh, H)))
         if not self.shares_cache:
@@ -99,7 +137,11 @@ class LatentAttention(Mixer):
     def bind(self, tensors, runtime: Runtime):
         nm, nh = self._name, self.n_heads
         self.act_dtype = runtime.act_dtype
-        ws = [tensors[nm("q")]]
+        ws = [tensors[nm("dq") if self.q_rank else nm("q")]]
+        self.q_up = self.q_norm_w = None
+        if self.q_rank:
+            self.q_up = Linear(tensors[nm("uq")], None, runtime.act_dtype)
+            self.q_norm_w = tensors[nm("dq_norm")].to(torch.float32).contiguous()
         if self.gated:
             ws.append(tensors[nm("g")])
         if not self.shares_cache:
@@ -112,8 +154,9 @@ class LatentAttention(Mixer):
         self.w_uk_t = tensors[nm("uk")].view(nh, self.dim, self.rank).transpose(1, 2).contiguous()
         self.w_uv = tensors[nm("uv")].view(nh, self.vdim, self.rank).contiguous()
         self.latent_norm_w = None if self.shares_cache else tensors[nm("dkv_norm")].to(torch.float32).contiguous()
-        i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
-        self.inv_freq = (self.rot_base ** (-2.0 * i / max(self.rot_dims, 1))).to(runtime.device)
+        self.open_gate = torch.full((1, nh), 30.0, dtype=runtime.act_dtype, device=runtime.device)
+        inv_freq, self.rot_magnitude = rescaled_frequencies(self.rot_dims, self.rot_base, self.rot_scaling)
+        self.inv_freq = inv_freq.to(runtime.device)
 
     def cache_need(self):
         if self.shares_cache:
@@ -157,18 +200,22 @@ class LatentAttention(Mixer):
                                "(and one that owns its cache must not)")
         T = ctx.n_tokens
         proj = self.in_proj.forward(x)
-        q = proj[:, : self.q_width]
-        at = self.q_width
+        if self.q_rank:      # queries through their own latent: norm (float32 statistics), then the up-projection
+            q = self.q_up.forward(ops.rmsnorm_rows(proj[:, : self.q_rank], self.q_norm_w, self.norm_eps))
+            at = self.q_rank
+        else:
+            q = proj[:, : self.q_width]
+            at = self.q_width
         if self.gated:
             gate = proj[:, at: at + nh]
             at += nh
-        else:       # sigmoid(+large) = 1
-            gate = torch.full((T, nh), 30.0, dtype=proj.dtype, device=proj.device)
+        else:       # sigmoid(+large) = 1: one constant row, read by every token (row stride 0)
+            gate = self.open_gate.expand(T, nh)
         dkv = None if self.shares_cache else proj[:, at: at + rank + dr]
         pages = self._pages(cache)
         ops.latent_prepare(q, dkv, self.latent_norm_w, self.inv_freq, ctx, cache.block_table,
                            None if self.shares_cache else pages, cache.page_size, nh, dn, dr, self.rot_dims, rank,
-                           self.norm_eps)
+                           self.norm_eps, neighbours=self.rot_pairing == "neighbours", magnitude=self.rot_magnitude)
         q3 = q.unflatten(1, (nh, dn + dr))
         qa = torch.empty((T, nh, rank), dtype=proj.dtype, device=proj.device)
         ops.gemm_batched(q3[:, :, :dn], self.w_uk_t, qa)

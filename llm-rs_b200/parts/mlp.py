@@ -29,15 +29,17 @@ class SwiGLU(FeedForward):
     fuses_residual = True
     ROLES = ("gate", "up", "down")
 
-    def __init__(self, hidden_size: int, intermediate_size: int, names=None, prefix: str = ""):
+    def __init__(self, hidden_size: int, intermediate_size: int, names=None, suffix: str = ".weight",
+                 prefix: str = ""):
         self.hidden_size, self.intermediate_size, self.prefix = hidden_size, intermediate_size, prefix
+        self.suffix = suffix        # what follows a role's name in the tensor's ("" for designs that name the matrix itself)
         self.names = {role: role for role in self.ROLES}
         self.names.update(names or {})
         if set(self.names) != set(self.ROLES):
             raise ValueError(f"names may rename {self.ROLES}, got {sorted(set(self.names) - set(self.ROLES))}")
 
     def _name(self, role: str) -> str:
-        return f"{self.prefix}{self.names[role]}.weight"
+        return f"{self.prefix}{self.names[role]}{self.suffix}"
 
     def weight_specs(self):
         H, I = self.hidden_size, self.intermediate_size

@@ -19,9 +19,11 @@ class DecoderModel:
         self.blocks = [build("block", layer.block, layer=layer) for layer in spec.layers]
         self.final_norm = build("norm", spec.final_norm)
         self.lm_head = build("lm_head", spec.lm_head)
+        self.reentry = build("reentry", spec.reentry) if spec.reentry is not None else None
 
     def parts(self):
-        return [self.embedding, *self.blocks, self.final_norm, self.lm_head]
+        extra = [self.reentry] if self.reentry is not None else []
+        return [self.embedding, *extra, *self.blocks, self.final_norm, self.lm_head]
 
     def weight_specs(self) -> List[WeightSpec]:
         seen: Dict[str, WeightSpec] = {}
@@ -66,9 +68,13 @@ class DecoderModel:
         h = self.embedding.forward(ctx.token_ids)
         pending = None
         order = self.spec.run_order
+        # What the passes over a looped stretch take from the embedding output is the same in every pass: made once.
+        entered = self.reentry.prepare(h, ctx) if self.reentry is not None else None
         for s, step in enumerate(order):
             block = self.blocks[step.layer]
-            after = self.blocks[order[s + 1].layer] if s + 1 < len(order) else None
+            if step.reenter:
+                h, pending = self.reentry.forward(h, pending, entered, ctx), None
+            after = self.blocks[order[s + 1].layer] if s + 1 < len(order) and not order[s + 1].reenter else None
             if (getattr(block, "links_norms", False) and getattr(after, "links_norms", False)
                     and after.accepts_prenormed(ctx.n_tokens)):
                 # The norm between the two blocks is spread over this block's last product and the next one's first.

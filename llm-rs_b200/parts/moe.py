@@ -23,7 +23,11 @@ class MixtureOfExperts(FeedForward):
     Router ``"table"``: no learned router; an integer table [vocab, top] names each token id's experts (the entries
     of a row differ), each weighted 1/top. Router ``"linear"``: logits ``W_router x + b`` as a float32 product (x may be
     its rounding to the activation type), the ``top`` largest are chosen (the lower expert among equals) and weighted
-    by the softmax over the chosen logits only. A router only fills (expert, weight) per assignment on the device; the
+    by the softmax over the chosen logits only. Router ``"softmax_bias"``: the same float32 logits without a bias, over
+    ``experts + n_identity`` outputs; scores ``s = softmax(logits)`` over all of them; the ``top`` largest ``s +
+    correction`` are chosen (``correction``: one stored number per output, which steers the choice only) and weighted
+    by ``s`` itself, not renormalised. The last ``n_identity`` outputs are identity experts: no tensors, their output
+    is the feed-forward's input times the weight. A router only fills (expert, weight) per assignment on the device; the
     grouping of rows by expert, the two grouped products and the weighted sum do not depend on which router ran.
 
     ``limit`` None leaves gate and up unclamped; with ``alpha`` 1 and ``up_shift`` 0 the unit is ``silu(g) * u``.
@@ -38,15 +42,21 @@ class MixtureOfExperts(FeedForward):
     ``<prefix>table`` unless ``names`` renames the roles."""
 
     reads_residual = True
-    ROLES = ("expert", "gate", "up", "down", "table", "router", "router_bias", "shared", "shared_gate")
+    ROLES = ("expert", "gate", "up", "down", "table", "router", "router_bias", "shared", "shared_gate", "correction")
+    ROUTERS = ("table", "linear", "softmax_bias")
 
     def __init__(self, hidden_size: int, expert_size: int, n_experts: int, top: int, vocab_size: int = 0,
                  router: str = "table", limit: Optional[float] = 1.0, alpha: float = 1.702, up_shift: float = 1.0,
-                 shared_size: int = 0, shared_gated: bool = False, names=None, prefix: str = ""):
-        if router not in ("table", "linear"):
-            raise ValueError(f"unknown router {router!r}; known: 'table', 'linear'")
-        if not 1 <= top <= n_experts:
-            raise ValueError(f"top {top} of {n_experts} experts")
+                 shared_size: int = 0, shared_gated: bool = False, n_identity: int = 0, names=None, prefix: str = ""):
+        if router not in self.ROUTERS:
+            raise ValueError(f"unknown router {router!r}; known: {self.ROUTERS}")
+        if n_identity and router != "softmax_bias":
+            raise ValueError(f"identity experts come with the router 'softmax_bias', not {router!r}")
+        if n_identity and shared_size:
+            raise ValueError("identity experts beside a shared expert: not built")
+        if not 1 <= top <= n_experts + n_identity:
+            raise ValueError(f"top {top} of {n_experts + n_identity} experts")
+        self.n_identity = int(n_identity)
         if router == "table" and vocab_size < 1:
             raise ValueError("the table router needs the vocabulary's size")
         self.hidden_size, self.expert_size, self.n_experts, self.top = hidden_size, expert_size, n_experts, top
@@ -56,7 +66,8 @@ class MixtureOfExperts(FeedForward):
         self.shared_size, self.shared_gated = int(shared_size), bool(shared_gated) and shared_size > 0
         self.prefix = prefix
         self.names = {"expert": "e{}.", "gate": "gate", "up": "up", "down": "down", "table": "table",
-                      "router": "router", "router_bias": "router.b", "shared": "shared.", "shared_gate": "shared.sg"}
+                      "router": "router", "router_bias": "router.b", "shared": "shared.", "shared_gate": "shared.sg",
+                      "correction": "correction"}
         self.names.update(names or {})
         if set(self.names) != set(self.ROLES):
             raise ValueError(f"names may rename {self.ROLES}, got {sorted(set(self.names) - set(self.ROLES))}")
@@ -73,9 +84,13 @@ class MixtureOfExperts(FeedForward):
         if self.router == "table":
             specs.append(WeightSpec(self.prefix + self.names["table"], (self.vocab_size, self.top),
                                     role="expert_table", limit=self.n_experts))
-        else:
+        elif self.router == "linear":
             specs += [WeightSpec(self.prefix + self.names["router"], (self.n_experts, H)),
                       WeightSpec(self.prefix + self.names["router_bias"], (self.n_experts,), role="bias")]
+        else:
+            n_all = self.n_experts + self.n_identity
+            specs += [WeightSpec(self.prefix + self.names["router"], (n_all, H)),
+                      WeightSpec(self.prefix + self.names["correction"], (n_all,), role="bias")]
         if self.shared_size:
             S, sp = self.shared_size, self.prefix + self.names["shared"]
             specs += [WeightSpec(sp + self.names["gate"], (S, H)), WeightSpec(sp + self.names["up"], (S, H)),
@@ -100,6 +115,11 @@ class MixtureOfExperts(FeedForward):
         if self.router == "linear":
             rows.append(tensors[self.prefix + self.names["router"]])
             bias.append(tensors[self.prefix + self.names["router_bias"]].to(torch.float32))
+        self.correction = None
+        if self.router == "softmax_bias":
+            rows.append(tensors[self.prefix + self.names["router"]])
+            bias.append(torch.zeros((rows[-1].size(0),), dtype=torch.float32, device=rows[-1].device))
+            self.correction = tensors[self.prefix + self.names["correction"]].to(torch.float32).contiguous()
         if self.shared_gated:       # the shared expert's gate is one more row of the router's product
             rows.append(tensors[self.prefix + self.names["shared_gate"]])
             bias.append(torch.zeros((1,), dtype=torch.float32, device=rows[-1].device))
@@ -123,16 +143,27 @@ class MixtureOfExperts(FeedForward):
                   if self.router_w is not None else None)
         if self.router == "table":
             expert_of, weight_of = ops.moe_route_table(ctx.token_ids, self.table, self.n_experts)
-        else:
+        elif self.router == "linear":
             expert_of, weight_of = ops.moe_route_top(logits, self.n_experts, self.top)
+        else:
+            expert_of, weight_of = ops.moe_route_biased(logits, self.correction, self.n_experts + self.n_identity,
+                                                        self.n_experts, self.top)
         n_rows = expert_of.numel()
         tile_rows = ops.grouped_tile_rows(n_rows, self.n_experts)
-        row_of, src_token, tiles, n_tiles = ops.moe_sort(expert_of, self.top, self.n_experts, tile_rows)
+        if self.n_identity:
+            # Assignments to identity experts are sorted into one more group that runs no product; the weighted sum
+            # takes the token's own row for them.
+            row_of, src_token, tiles, n_tiles = ops.moe_sort(expert_of, self.top, self.n_experts + 1, tile_rows,
+                                                             tiled_groups=self.n_experts)
+        else:
+            row_of, src_token, tiles, n_tiles = ops.moe_sort(expert_of, self.top, self.n_experts, tile_rows)
         act = torch.empty((n_rows, self.expert_size), dtype=self.act_dtype, device=x.device)
         ops.gemm_grouped(x, self.w_gate, act, tiles, n_tiles, src_token, w2=self.w_up, limit=self.limit,
                          alpha=self.alpha, shift=self.up_shift, tile_rows=tile_rows)
         rows = torch.empty((n_rows, self.hidden_size), dtype=torch.float32, device=x.device)
         ops.gemm_grouped(act, self.w_down, rows, tiles, n_tiles, None, tile_rows=tile_rows)
+        if self.n_identity:
+            return ops.moe_combine_identity(rows, row_of, weight_of, expert_of, x, self.top, self.n_experts)
         if self.shared is None:
             return ops.moe_combine(rows, row_of, weight_of, self.top)
         gate = logits[:, logits.size(1) - 1] if self.shared_gated else None

@@ -1,5 +1,5 @@
 """Registries of parts by kind: mixers, feed-forwards, norms, position encodings, blocks,
-embeddings and heads. ``build(kind_of_part, spec, ...)`` makes the part a ``PartSpec`` names.
+embeddings, heads and re-entries of the embedding output. ``build(kind_of_part, spec, ...)`` makes the part a ``PartSpec`` names.
 
 A part class is registered with ``@register("mixer", "gqa_attention")``. Tests register
 toy parts the same way; the framework's files need no change for a new part.
@@ -8,7 +8,7 @@ from __future__ import annotations
 
 from typing import Any, Callable, Dict
 
-_CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "lm_head")
+_CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "lm_head", "reentry")
 _REGISTRY: Dict[str, Dict[str, Callable[..., Any]]] = {c: {} for c in _CATEGORIES}
 
 

@@ -27,7 +27,8 @@ class ScoredAttention(Mixer):
     q, k, v projections (no biases) -> RMS norm over the WHOLE q row and the whole k row, all heads at once, with
     plain weights of that size (``qk_norm`` "whole"; "none": no norm) -> rotation of the first ``rot_dims`` channels
     of every head, channel i paired with i + rot_dims/2, angle position * rot_base^(-2i/rot_dims) (q and k, not v)
-    -> new keys and values into the pages -> score = (q . k) * ``scale``, then ``softcap * tanh(score / softcap)``
+    -> with ``qk_norm`` "head_unit": every head of q and k divided by its own root mean square, AFTER the rotation,
+    without a weight -> new keys and values into the pages -> score = (q . k) * ``scale``, then ``softcap * tanh(score / softcap)``
     when ``softcap`` > 0 -> mask: causal, and with ``mask`` "window" the last ``mask_size`` keys, with "chunk" only
     keys of the query's own chunk of ``mask_size`` positions (chunks counted from position 0 of the sequence) ->
     softmax whose denominator also holds exp(sink_h), one learned number per query head (``sink``; it has no key
@@ -39,19 +40,19 @@ class ScoredAttention(Mixer):
     on the tensor cores in bfloat16 (``csrc/attention_scored.cu``: ``mma.sync``; long portions of heads of 128
     channels: the tcgen05 kernel of ``csrc/attention_tc.cu``, which takes the cap, the sink and the mask in its
     softmax; ``LLMRS_ATTN_TC=0`` keeps ``mma.sync``); requests that bring one token take the decode kernel in the
-    same step. ``names`` maps the roles q, k, v, o, q_norm, k_norm, sink."""
-    ROLES = ("q", "k", "v", "o", "q_norm", "k_norm", "sink")
+    same step. ``names`` maps the roles q, k, v, o, q_norm, k_norm, sink, g."""
+    ROLES = ("q", "k", "v", "o", "q_norm", "k_norm", "sink", "g")
 
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float,
                  softcap: float = 0.0, sink: bool = False, mask: str = "causal", mask_size: int = 0,
                  qk_norm: str = "whole", norm_eps: float = 1e-6, rot_dims: int = 0, rot_base: float = 10000.0,
-                 names=None, prefix: str = ""):
+                 gated: bool = False, names=None, prefix: str = ""):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} query heads are no multiple of {n_kv_heads} key/value heads")
         if mask not in MASKS or (mask != "causal" and mask_size < 1):
             raise ValueError(f"mask {mask!r} of size {mask_size}; known masks: {sorted(MASKS)}")
-        if qk_norm not in ("whole", "none"):
-            raise ValueError(f"unknown qk_norm {qk_norm!r}; known: 'whole', 'none'")
+        if qk_norm not in ("whole", "none", "head_unit"):
+            raise ValueError(f"unknown qk_norm {qk_norm!r}; known: 'whole', 'none', 'head_unit'")
         if rot_dims % 2 or not 0 <= rot_dims <= dim:
             raise ValueError(f"rot_dims {rot_dims} must be even and at most dim {dim}")
         if not (1 <= dim <= 256 and 1 <= vdim <= 256):
@@ -61,8 +62,10 @@ class ScoredAttention(Mixer):
         self.mask, self.mask_size = mask, int(mask_size) if mask != "causal" else 0
         self.qk_norm, self.norm_eps = qk_norm, float(norm_eps)
         self.rot_dims, self.rot_base = int(rot_dims), float(rot_base)
+        self.gated = bool(gated)
         self.prefix = prefix
-        self.names = {"q": "q", "k": "k", "v": "v", "o": "o", "q_norm": "q.norm", "k_norm": "k.norm", "sink": "sink"}
+        self.names = {"q": "q", "k": "k", "v": "v", "o": "o", "q_norm": "q.norm", "k_norm": "k.norm", "sink": "sink",
+                      "g": "g"}
         self.names.update(names or {})
         if set(self.names) != set(self.ROLES):
             raise ValueError(f"names may rename {self.ROLES}, got {sorted(set(self.names) - set(self.ROLES))}")
@@ -80,16 +83,27 @@ class ScoredAttention(Mixer):
                       WeightSpec(nm("k_norm"), (self.k_width,), role="norm")]
         if self.has_sink:
             specs.append(WeightSpec(nm("sink"), (self.n_heads,), role="bias"))
+        if self.gated:
+            specs.append(WeightSpec(nm("g"), (self.n_heads, H)))
         return specs
 
     def bind(self, tensors, runtime: Runtime):
         nm = self._name
         self.act_dtype = runtime.act_dtype
         ws = [tensors[nm(r)] for r in "qkv"]
+        if self.gated:
+            # The gates' rows follow v's in the same product; zero rows fill up to a multiple of eight, so that a
+            # product whose width fitted the tensor-core kernels still does.
+            g = tensors[nm("g")]
+            fill = -(self.q_width + self.k_width + self.v_width + self.n_heads) % 8
+            ws += [g, g.new_zeros((fill, g.size(1)))] if fill else [g]
         dt = ws[0].dtype if all(w.dtype == ws[0].dtype for w in ws) else torch.float32
         wqkv = torch.cat([w.to(dt) for w in ws], dim=0).contiguous()
         self.qkv_proj = Linear(wqkv, None, runtime.act_dtype)
-        self.q_proj = Linear(wqkv[: self.q_width], None, runtime.act_dtype)     # for entries that read another's pages
+        # For entries that read another's pages: the queries (and the gates) alone.
+        wq = wqkv[: self.q_width] if not self.gated else torch.cat(
+            [wqkv[: self.q_width], wqkv[self.q_width + self.k_width + self.v_width:]], dim=0).contiguous()
+        self.q_proj = Linear(wq, None, runtime.act_dtype)
         self.o_proj = Linear(tensors[nm("o")], None, runtime.act_dtype)
         f32 = lambda role: tensors[nm(role)].to(torch.float32).contiguous()
         self.q_norm_w = f32("q_norm") if self.qk_norm == "whole" else None
@@ -121,13 +135,17 @@ class ScoredAttention(Mixer):
             qkv = self.qkv_proj.forward(x)
             q = qkv[:, : self.q_width]
             k = qkv[:, self.q_width: self.q_width + self.k_width]
-            v = qkv[:, self.q_width + self.k_width:]
+            at = self.q_width + self.k_width + self.v_width
+            v = qkv[:, self.q_width + self.k_width: at]
+            gate = qkv[:, at: at + self.n_heads] if self.gated else None
         else:
-            q, k, v = self.q_proj.forward(x), None, None
+            qg = self.q_proj.forward(x)
+            q, k, v = qg[:, : self.q_width], None, None
+            gate = qg[:, self.q_width: self.q_width + self.n_heads] if self.gated else None
         pages = _pages(cache)
         ops.scored_prepare(q, k, v, self.q_norm_w, self.k_norm_w, self.inv_freq, ctx, table,
                            pages if cache.owns else None, self.n_heads, self.n_kv_heads, self.dim, self.vdim,
-                           self.rot_dims, cache.page_size, self.norm_eps)
+                           self.rot_dims, cache.page_size, self.norm_eps, unit_heads=self.qk_norm == "head_unit")
         out = torch.empty((ctx.n_tokens, self.n_heads * self.vdim), dtype=q.dtype, device=q.device)
         plan = ctx.plan(self.plan_key())
         n_tiles, n_decode, max_kv = (plan.values[key] for key in ("n_prefill_tiles", "n_decode", "max_decode_kv_len"))
@@ -147,6 +165,8 @@ class ScoredAttention(Mixer):
                 split_keys *= 2
             ops.scored_decode(q, out, pages, plan.arrays["decode_reqs"], n_decode, ctx, table, -(-span // split_keys),
                               split_keys, *args)
+        if gate is not None:
+            ops.head_gate(out, gate, self.n_heads, self.vdim)
         return self.o_proj.forward(out)
 
 

@@ -45,10 +45,12 @@ class RunStep:
     ``layer`` indexes ``ModelSpec.layers`` (a layer may be named by several entries: its
     weights are shared, each entry has a cache of its own). ``cache_of`` names an
     EARLIER entry of the run order whose cache this entry reads instead of owning one;
-    such an entry writes no keys or values.
+    such an entry writes no keys or values. ``reenter``: before this entry runs, the stream is mixed with the
+    embedding output by the model's ``reentry`` part (the first entry of a pass over a looped stretch of layers).
     """
     layer: int
     cache_of: Optional[int] = None
+    reenter: bool = False
 
 
 @dataclass(frozen=True)
@@ -62,8 +64,11 @@ class ModelSpec:
     lm_head: PartSpec
     max_positions: int
     eos_token_ids: Tuple[int, ...] = ()
+    reentry: Optional[PartSpec] = None       # the part that run-order entries with ``reenter`` call
 
     def validate(self) -> None:
+        if self.reentry is None and any(step.reenter for step in self.run_order):
+            raise ValueError("a run-order entry re-enters the embedding output, but the model names no reentry part")
         for s, step in enumerate(self.run_order):
             if not 0 <= step.layer < len(self.layers):
                 raise ValueError(f"run_order[{s}] names layer {step.layer}, model has {len(self.layers)}")
