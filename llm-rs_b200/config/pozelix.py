@@ -10,7 +10,7 @@ none), every branch between two norms; a stretch of the layers may run several t
     attention mixer:         heads, kv_heads, dim, vdim, scale, mask.size (optional: a sliding window),
                              rot.base, rot.dims (optional: no rotation without them)
     latent_attention mixer:  heads, dim, rot_dim, vdim, kv_rank, q_rank, scale, rot.base, rot.dims,
-                             rot.scaling {factor, original, fast, slow} (optional)
+                             rot.scaling {factor, original, fast, slow} (optional), mask.size (optional)
     mlp:                     kind "dense": ff
                              kind "moe":   expert.ff, router.experts, router.top, router.identity (optional)
 
@@ -72,13 +72,17 @@ class LatentMixer:
     rot_base: float
     rot_dims: int
     scaling: Optional[RotScaling] = None
+    window: int = 0      # mask.size, as in the other mixer; 0 (no mask key): every earlier token is seen
 
     def to_dict(self) -> Dict[str, Any]:
         rot: Dict[str, Any] = {"base": self.rot_base, "dims": self.rot_dims}
         if self.scaling is not None:
             rot["scaling"] = self.scaling.to_dict()
-        return {"heads": self.heads, "dim": self.dim, "rot_dim": self.rot_dim, "vdim": self.vdim,
-                "kv_rank": self.kv_rank, "q_rank": self.q_rank, "scale": self.scale, "rot": rot}
+        d = {"heads": self.heads, "dim": self.dim, "rot_dim": self.rot_dim, "vdim": self.vdim,
+             "kv_rank": self.kv_rank, "q_rank": self.q_rank, "scale": self.scale, "rot": rot}
+        if self.window:
+            d["mask"] = {"size": self.window}
+        return d
 
 
 @dataclass(frozen=True)
@@ -171,8 +175,6 @@ class PozelixConfig:
                 rot_dims = rot_dim if rot_dims is None else rot_dims
                 if rot_dims % 2 or rot_dims > rot_dim:
                     raise ConfigError(f"{where}: rot.dims {rot_dims} must be even and at most rot_dim {rot_dim}")
-                if m.get("mask") is not None:
-                    raise ConfigError(f"{where}: a latent_attention layer sees every earlier token (no mask)")
                 scaling = None
                 sc = m["rot"].get("scaling") if isinstance(m.get("rot"), Mapping) else None
                 if sc is not None:
@@ -187,7 +189,7 @@ class PozelixConfig:
                     heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=_get(m, "kv_rank", int, where, 1),
                     q_rank=_get(m, "q_rank", int, where, 1), scale=scale,
                     rot_base=(_get(m, "rot.base", float, where) if rot_dims else 1.0), rot_dims=rot_dims,
-                    scaling=scaling)
+                    scaling=scaling, window=_get(m, "mask.size", int, where, 1, optional=True) or 0)
             mlp_raw, mlp = lr.get("mlp"), None
             if mlp_raw is not None:
                 if not isinstance(mlp_raw, Mapping) or mlp_raw.get("kind") not in ("dense", "moe"):

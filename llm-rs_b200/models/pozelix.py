@@ -3,7 +3,7 @@
 Every layer is a ``sandwich`` block (a norm ahead of each branch and one on its output) around one of two mixers:
 ``scored_attention`` with a sliding window, rotation by halves, unit-norm heads after the rotation and a sigmoid gate
 per head, or ``latent_attention`` with queries through a latent of their own, rotation of neighbouring pairs and
-rescaled frequencies, every earlier token visible, no gate. The feed-forward is the gated SiLU unit, dense or as routed
+rescaled frequencies, every earlier token visible unless the layer names a window, no gate. The feed-forward is the gated SiLU unit, dense or as routed
 experts whose router scores all experts by a softmax, chooses by score plus a stored correction and may name identity
 experts. A stretch of layers may run several times with the same weights: every pass has run-order entries (so pages)
 of its own and starts by mixing the stream with the embedding output (``embedding_mix``).
@@ -55,7 +55,7 @@ def build_spec(cfg: PozelixConfig) -> ModelSpec:
                 "hidden_size": D, "n_heads": m.heads, "dim": m.dim, "rot_dim": m.rot_dim, "vdim": m.vdim,
                 "rank": m.kv_rank, "q_rank": m.q_rank, "scale": m.scale, "rot_base": m.rot_base,
                 "rot_dims": m.rot_dims, "rot_pairing": "neighbours",
-                "rot_scaling": None if m.scaling is None else m.scaling.to_dict(), "window": 0,
+                "rot_scaling": None if m.scaling is None else m.scaling.to_dict(), "window": m.window,
                 "norm_eps": cfg.norm_eps, "gated": False})
         f, ffn = layer.mlp, None
         if isinstance(f, DenseMLP):

@@ -117,7 +117,7 @@ def latent_attention(h, m, w, p, eps):
     v = (c @ w[p + "uv"].T).view(T, H, dv)
     qq = torch.cat([q[..., :d], qr], dim=-1)
     kk = torch.cat([kn, kr.expand(T, H, dr)], dim=-1)
-    o = softmax_attention(qq, kk, v, m["scale"], 0)
+    o = softmax_attention(qq, kk, v, m["scale"], (m.get("mask") or {}).get("size", 0))
     return o.reshape(T, H * dv) @ w[p + "o"].T
 
 
@@ -188,3 +188,15 @@ def forward(tokens, cfg, w, residuals=None):
         if residuals is not None:
             residuals.append(x)
     return rms_norm(x, w["final.norm"], cfg["norm"]["eps"]) @ w["head"].T
+
+
+def load_model_dir(path: str):
+    """(config dict, {name: float64 tensor}) of a model folder."""
+    import json
+    import os
+
+    from plain_rusadra import read_safetensors
+    with open(os.path.join(path, "config.json")) as f:
+        cfg = json.load(f)
+    w = read_safetensors(os.path.join(path, "model.safetensors"))
+    return cfg, {k: v.to(F64) for k, v in w.items()}
