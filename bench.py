@@ -20,7 +20,8 @@ A "step" is one decode step of the whole batch. The default is batch 8 at a cont
 The K timed steps run back to back as five runs of K/5 steps with a CUDA event between them: ``value`` and
 ``ms_per_step`` are the median run's, ``repeats`` gives the runs' spread and the mean over all K steps.
 ``--workload rusadra`` measures the Rusadra design beside Qwen3 at equal size instead (see DESIGN_SIZES below), and
-``--workload pusazen`` the Pusazen design beside Rusadra; the default workload and its JSON line are unchanged by them.
+``--workload pusazen`` the Pusazen design beside Rusadra, ``--workload pozelix`` the Pozelix design beside both; the
+default workload and its JSON line are unchanged by them.
 Fractions are given against two denominators: the peaks measured on this pool (MEASURED_PEAKS.json beside
 this file when present, else 6.65 TB/s and 1.59 PFLOP/s) and the nominal figures of the part (7.7 TB/s,
 2.25 PFLOP/s dense bf16). Only N = 1 is supported: the engine is a single-GPU engine.
@@ -105,6 +106,31 @@ def pusazen_configs(z):
            "postln_alpha": 2.0, "logit_scale": 0.5,
            "layers": [dict(order[i % 4], mlp=mlp) for i in range(z["layers"])]}
     return pus, design_configs(z)[0]
+
+
+# ``--workload pozelix``: the Pozelix design (window attention with unit-norm heads and a gate per head and latent
+# attention with a query latent in turn, norms on both sides of every branch, dense and routed feed-forwards in turn with
+# a router that scores all experts and two identity experts, the first quarter of the layers run twice) beside the
+# Rusadra design (latent attention, routed experts) and the Pusazen design (attention with options on the score, a
+# learned router) at equal width, layer runs, vocabulary, experts and expert width; the same measurements.
+def pozelix_configs(z):
+    """(Pozelix config.json, Rusadra config.json, Pusazen config.json) of one entry of DESIGN_SIZES."""
+    window = {"type": "attention", "mixer": {
+        "heads": z["heads"], "kv_heads": max(1, z["heads"] // 4), "dim": z["dim"], "vdim": z["vdim"],
+        "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}, "rot": {"base": 1e6, "dims": z["dim"]}}}
+    latent = {"type": "latent_attention", "mixer": {
+        "heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["rank"],
+        "q_rank": 3 * z["rank"] // 2, "scale": (z["dim"] + z["rot"]) ** -0.5,
+        "rot": {"base": 1e4, "dims": z["rot"], "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    dense = {"kind": "dense", "ff": z["top"] * z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "identity": 2}}
+    twice = max(1, z["layers"] // 4)
+    poz = {"architecture": "Pozelix", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+           "loop": {"start": 0, "stop": twice, "times": 2},
+           "layers": [dict(window if i % 2 == 0 else latent, mlp=moe if i % 2 == 0 else dense)
+                      for i in range(z["layers"] - twice)]}
+    return poz, design_configs(z)[0], pusazen_configs(z)[0]
 
 
 def run_design(args, configs=None, workload="rusadra"):
@@ -398,7 +424,7 @@ def main():
     ap.add_argument("--profile", action="store_true", help="instead of the benchmark: time every kernel class of one "
                     "decode step and of the prefill with CUDA events (eager launches, NVTX ranges) and print a table "
                     "with bytes, flops and the fraction of the peaks to standard error, the rows as JSON to standard output")
-    ap.add_argument("--workload", default="decode", choices=["decode", *WORKLOADS, "rusadra", "pusazen"],
+    ap.add_argument("--workload", default="decode", choices=["decode", *WORKLOADS, "rusadra", "pusazen", "pozelix"],
                     help="decode: the benchmark contract (default). mixed14b / stress32b: a whole serving run "
                     "through the engine on the layer sizes of Qwen3-14B / Qwen3-32B. rusadra: prefill and decode of the "
                     "Rusadra design beside Qwen3 at equal width, depth, vocabulary and active feed-forward width, with "
@@ -418,6 +444,8 @@ def main():
         return 2
     if args.workload == "pusazen":
         return run_design(args, pusazen_configs, "pusazen")
+    if args.workload == "pozelix":
+        return run_design(args, pozelix_configs, "pozelix")
     if args.workload == "rusadra":
         return run_design(args)
     if args.workload != "decode":

@@ -164,6 +164,10 @@ WRAPPED: Dict[str, Callable] = {
     "add_rmsnorm": _cost_rows(0), "embedding": lambda table, ids, *a, **k: ("", ids.numel() * table.size(1) * (table.element_size() + 4), 0.0),
     "silu_mul": _cost_rows(0), "qk_norm_rope_kvwrite": _cost_rows(0, 1, 2), "residual_add": _cost_rows(0, 1),
     "argmax": _cost_rows(0), "sample": _cost_rows(0), "scatter_tokens": _cost_rows(0),
+    "outnorm_add_norm": lambda h, y, *a, **k: ("", 2 * _nbytes(h) + 2 * _nbytes(y), 0.0),
+    "head_gate": _cost_rows(0), "rmsnorm_rows": _cost_rows(0), "moe_route_biased": _cost_rows(0),
+    "moe_combine_identity": lambda rows, row_of, weight_of, expert_of, x, *a, **k: (
+        "", _nbytes(rows, x) + x.size(0) * x.size(1) * 4, 0.0),
 }
 
 

@@ -54,13 +54,14 @@ POZELIX_A = {
         (_latent(2, 24, 4, 8, 32, 48, 0.15, 500.0), _moe(24, 3, 3)))}
 
 # Attention first; one key head for five query heads; a window of 7 (shorter than a page of 8) and a window of ONE key;
-# a rotated part of 2 entries; one expert of five; more identity experts than real ones with every output chosen; no loop.
+# a rotated part of 2 entries; more identity experts than real ones with every output chosen; one expert of five in the
+# last layer (a pick that rounding turns then moves that token's logits only, not every later one's); no loop.
 POZELIX_B = {
     "architecture": "Pozelix", "vocab": 157, "width": 72, "norm": {"eps": 1e-6},
     "layers": _layers(
-        (_window(5, 1, 24, 8, 0.25, window=7, rot=(500.0, 24)), _moe(56, 5, 1)),
+        (_window(5, 1, 24, 8, 0.25, window=7, rot=(500.0, 24)), _moe(30, 2, 5, identity=3)),
         (_latent(2, 8, 2, 40, 64, 8, 0.3, 10000.0), _dense(50)),
-        (_window(2, 2, 8, 40, 0.4, window=1), _moe(30, 2, 5, identity=3)))}
+        (_window(2, 2, 8, 40, 0.4, window=1), _moe(56, 5, 1)))}
 
 # Sizes at which the bfloat16 engine's kernels take the tensor cores (multiples of 16 and 64): latents of 128 and 64,
 # heads of 64 and 128, windows of 48 and 130, eight experts; the first two layers run twice.

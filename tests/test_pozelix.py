@@ -158,3 +158,95 @@ def test_rescaled_frequencies_against_plain(dims, base, scaling):
             assert abs(float(f[i] / plain[i]) - 1.0 / sc["factor"]) < 1e-12
         else:
             assert 1.0 / sc["factor"] - 1e-12 <= float(f[i] / plain[i]) <= 1.0 + 1e-12
+
+
+# ---- the plain implementation's own properties ------------------------------------------------------
+def _random_mixer_weights(names_shapes, seed):
+    g = torch.Generator().manual_seed(seed)
+    return {n: torch.randn(shape, generator=g, dtype=F64) / math.sqrt(shape[-1]) for n, shape in names_shapes.items()}
+
+
+def test_plain_window_sees_itself_and_the_tokens_before_it_only():
+    m = {"heads": 2, "kv_heads": 1, "dim": 8, "vdim": 6, "scale": 0.4, "mask": {"size": 5}, "rot": {"base": 100.0, "dims": 4}}
+    w = _random_mixer_weights({"m.q": (16, 12), "m.k": (8, 12), "m.v": (6, 12), "m.g": (2, 12), "m.o": (12, 12)}, 1)
+    x = torch.randn(30, 12, generator=torch.Generator().manual_seed(2), dtype=F64)
+    base = P.window_attention(x, m, w, "m.", 1e-6)
+    other = x.clone()
+    other[10] = 9.0 * torch.randn(12, generator=torch.Generator().manual_seed(3), dtype=F64)
+    moved = (P.window_attention(other, m, w, "m.", 1e-6) - base).abs().amax(dim=1)
+    assert bool((moved[:10] == 0).all()) and bool((moved[15:] == 0).all())      # 10 is seen by 10 .. 14
+    assert bool((moved[10:15] > 1e-6).all())
+    # A window of one key: every token sees itself only, so its row depends on nothing else.
+    m1 = dict(m, mask={"size": 1})
+    alone = torch.cat([P.window_attention(x[i:i + 1], dict(m1, rot=None), w, "m.", 1e-6) for i in range(4)])
+    assert torch.allclose(P.window_attention(x[:4], dict(m1, rot=None), w, "m.", 1e-6), alone, atol=1e-12)
+
+
+def test_plain_unit_norm_heads_forget_the_size_of_q_and_k_and_a_shut_gate_closes_a_head():
+    m = {"heads": 2, "kv_heads": 2, "dim": 8, "vdim": 6, "scale": 0.4, "rot": {"base": 100.0, "dims": 8}}
+    w = _random_mixer_weights({"m.q": (16, 12), "m.k": (16, 12), "m.v": (12, 12), "m.g": (2, 12), "m.o": (12, 12)}, 4)
+    x = torch.randn(9, 12, generator=torch.Generator().manual_seed(5), dtype=F64)
+    base = P.window_attention(x, m, w, "m.", 0.0)
+    big = dict(w)
+    big["m.q"], big["m.k"] = 7.0 * w["m.q"], 0.01 * w["m.k"]
+    assert torch.allclose(P.window_attention(x, m, big, "m.", 0.0), base, atol=1e-10)
+    # With head 1's gate row zeroed its gate is sigmoid(0) = 1/2 everywhere: that isolates the head's ungated output.
+    shut = dict(w)
+    shut["m.g"] = w["m.g"].clone()
+    shut["m.g"][1] = 0.0
+    half = P.window_attention(x, m, shut, "m.", 0.0)          # sigmoid(0) = 1/2 on head 1
+    no_head = dict(w)
+    no_head["m.o"] = w["m.o"].clone()
+    no_head["m.o"][:, 6:] = 0.0
+    only0 = P.window_attention(x, m, no_head, "m.", 0.0)
+    gate1 = torch.sigmoid(x @ w["m.g"][1])
+    # out = head0 + gate1 * head1' ; with the zeroed gate row: head0 + head1' / 2
+    head1 = (half - only0) * 2.0
+    assert torch.allclose(base, only0 + gate1[:, None] * head1, atol=1e-10)
+
+
+def test_plain_pairings_and_magnitude():
+    x = torch.zeros(1, 1, 8, dtype=F64)
+    x[0, 0, 0] = 1.0
+    pos = torch.tensor([3])
+    near = P.rotate(x, pos, 4, 10.0, "neighbours")[0, 0]
+    half = P.rotate(x, pos, 4, 10.0, "half")[0, 0]
+    assert abs(float(near[0]) - math.cos(3.0)) < 1e-12 and abs(float(near[1]) - math.sin(3.0)) < 1e-12
+    assert abs(float(half[0]) - math.cos(3.0)) < 1e-12 and abs(float(half[2]) - math.sin(3.0)) < 1e-12
+    assert float(near[2:].abs().max()) == 0.0 and float(half[1]) == 0.0 and float(half[3:].abs().max()) == 0.0
+    sc = {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 1.0}
+    scaled = P.rotate(x, pos, 4, 10.0, "neighbours", sc)[0, 0]
+    assert abs(float(scaled[:2].norm()) - (0.1 * math.log(4.0) + 1.0)) < 1e-12      # cos and sin times the magnitude
+
+
+def test_plain_correction_steers_the_choice_and_not_the_weight_and_identity_experts_return_their_input():
+    f = {"kind": "moe", "expert": {"ff": 5}, "router": {"experts": 2, "top": 1, "identity": 1}}
+    g = torch.Generator().manual_seed(6)
+    w = {"f.router": torch.randn(3, 4, generator=g, dtype=F64), "f.correction": torch.zeros(3, dtype=F64)}
+    for e in range(2):
+        w.update({f"f.e{e}.gate": torch.randn(5, 4, generator=g, dtype=F64), f"f.e{e}.up": torch.randn(5, 4, generator=g, dtype=F64),
+                  f"f.e{e}.down": torch.randn(4, 5, generator=g, dtype=F64)})
+    h = torch.randn(6, 4, generator=g, dtype=F64)
+    s = torch.softmax(h @ w["f.router"].T, dim=-1)
+    w["f.correction"] = torch.tensor([0.0, 0.0, 2.0], dtype=F64)      # the identity expert wins everywhere
+    chosen, weights = P.route(h, f, w, "f.")
+    assert chosen.flatten().tolist() == [2] * 6 and torch.allclose(weights[:, 0], s[:, 2])
+    assert torch.allclose(P.routed_experts(h, f, w, "f."), s[:, 2:3] * h)
+    w["f.correction"] = torch.tensor([2.0, 0.0, 0.0], dtype=F64)
+    assert torch.allclose(P.routed_experts(h, f, w, "f."), s[:, 0:1] * P.gated_unit(h, w, "f.e0."))
+
+
+def test_plain_every_pass_of_a_loop_re_enters_through_the_embedding(tmp_path):
+    cfg, w = P.load_model_dir(write_pozelix_model("E", str(tmp_path)))
+    toks = list(range(3, 40))
+    ref = P.forward(toks, cfg, w)
+    once = json.loads(json.dumps(cfg))
+    once["loop"]["times"] = 1
+    assert float((P.forward(toks, once, w) - ref).abs().max()) > 1e-2
+    blind = dict(w)
+    blind["loop.in"] = w["loop.in"].clone()
+    blind["loop.in"][:, cfg["width"]:] = 0.0
+    assert float((P.forward(toks, cfg, blind) - ref).abs().max()) > 1e-2
+    res = []
+    P.forward(toks, cfg, w, res)
+    assert len(res) == 6      # layer 0, four passes of layer 1, layer 2

@@ -1,0 +1,567 @@
+"""The Pozelix design on the GPU against the plain implementation (tests/plain_pozelix.py, float64, no cache): each
+mechanism's kernels alone (the norms around a branch in one pass, the stream's re-entry through the embedding, window
+attention with unit-norm heads and a gate per head, latent attention with a query latent and rescaled neighbour pairs,
+the router that scores all experts, identity experts), then whole models replayed whole, with a tail decoded token by
+token, in portions down to one and two tokens and in mixed batches with so few pages and slots that they are used
+again; float32 and bfloat16; greedy generation through the engine's entry point and scheduler, with and without CUDA
+graphs; the trace program and the command line."""
+import json
+import math
+import os
+import subprocess
+import sys
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+import plain_pozelix as P
+import replay_util as RU
+from pozelix_configs import POZELIX, write_pozelix_model
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 2e-4          # float32 engine against float64: rounding only
+TOL_BF16_REL = 0.05     # of the largest logit; a wrong key, window or expert moves logits by their own size
+DEV = "cuda:0"
+LENGTHS = {"A": [2, 19, 40, 77, 131, 260], "B": [1, 9, 33, 70, 128, 161], "C": [5, 31, 66, 150, 300],
+           "D": [1, 2, 18, 65, 140, 700], "E": [3, 16, 47, 90, 200], "F": [1, 6, 29, 64, 133, 210]}
+MODES = ["whole", "tail", "portions", "mixed"]
+FRAGILE = {}      # model name -> {(request, position)} that bfloat16 cannot be held to (see _fragile_positions)
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    folder = tmp_path_factory.mktemp("pozelix")
+    out = {}
+    for name in POZELIX:
+        path = write_pozelix_model(name, str(folder))
+        cfg, w = P.load_model_dir(path)
+        rng = np.random.default_rng(17 + ord(name))
+        reqs = {f"r{i}": rng.integers(0, cfg["vocab"], n).tolist() for i, n in enumerate(LENGTHS[name])}
+        ref = {r: P.forward(toks, cfg, w).numpy() for r, toks in reqs.items()}
+        out[name] = (path, cfg, w, reqs, ref)
+        FRAGILE[name] = _fragile_positions(cfg, w, reqs, ref)
+    return out
+
+
+def _fragile_positions(cfg, w, reqs, ref):
+    """Positions whose logits move by more than half the bfloat16 tolerance when every matrix is disturbed by relative
+    noise of bfloat16's rounding size (2^-9), in the plain implementation itself: a router's pick between two nearly
+    equal choice scores turns under rounding, and the token then runs other experts. The float32 engine is held to
+    every position; the bfloat16 engine to all but these (a bounded share)."""
+    g = torch.Generator().manual_seed(99)
+    noisy = {k: (v * (1.0 + 2.0 ** -9 * torch.randn(v.shape, generator=g, dtype=v.dtype)) if v.dim() == 2 else v)
+             for k, v in w.items()}
+    scale = max(float(np.abs(r).max()) for r in ref.values())
+    fragile = set()
+    for r, toks in reqs.items():
+        moved = np.abs(P.forward(toks, cfg, noisy).numpy() - ref[r]).max(axis=1)
+        fragile |= {(r, int(p)) for p in np.nonzero(moved > 0.5 * TOL_BF16_REL * scale)[0]}
+    assert len(fragile) <= 0.2 * sum(len(t) for t in reqs.values()), "too many ill-conditioned positions for a test"
+    return fragile
+
+
+class _Ctx(SimpleNamespace):
+    """The index arrays of a step, as the step function gives them to the parts, with a mixer's plan and workspace."""
+
+    def plan(self, key):
+        return self.plans[key]
+
+    def scratch(self, name, n_floats):
+        return torch.zeros((max(n_floats, 1),), dtype=torch.float32, device=DEV)
+
+
+def _ctx(n_new, cached, slots=None, planner=None, page_size=16):
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    q_start = np.concatenate([[0], np.cumsum(n_new)[:-1]]).tolist()
+    token_req = [r for r, n in enumerate(n_new) for _ in range(n)]
+    positions = [c + i for c, n in zip(cached, n_new) for i in range(n)]
+    slots = list(slots if slots is not None else range(len(n_new)))
+    ctx = _Ctx(n_tokens=sum(n_new), n_requests=len(n_new), q_start=i32(q_start), n_new=i32(n_new),
+               cached_len=i32(cached), slot_ids=i32(slots), token_req=i32(token_req), positions=i32(positions), plans={})
+    if planner is not None and hasattr(planner, "plan"):
+        from llm_rs_b200.parts.base import StepInfo
+        a32 = lambda v: np.asarray(v, np.int32)
+        plan = planner.plan(StepInfo(sum(n_new), len(n_new), a32(q_start), a32(n_new), a32(cached), a32(slots),
+                                     [], [], page_size, False))
+        ctx.plans[planner.plan_key()] = SimpleNamespace(
+            arrays={k: torch.from_numpy(np.ascontiguousarray(v)).to(DEV) for k, v in plan.arrays.items()},
+            values=dict(plan.values))
+    return ctx
+
+
+def _assert_logits(got, ref, dtype, what, fragile=()):
+    """float32: every position within TOL_F32 (this pins the logic). bfloat16: the positions in ``fragile`` are left
+    out; of the others three in a hundred may exceed the tolerance (one noise draw does not find every pick of a router
+    that rounding can turn). A wrong key, window or expert in a bfloat16 kernel moves every later position."""
+    scale = max(float(np.abs(r).max()) for r in ref.values())
+    diffs = {k: float(np.abs(row.astype(np.float64) - ref[k[0].replace("again", "")][k[1]]).max())
+             for k, row in got.items()}
+    assert all(np.isfinite(d) for d in diffs.values()), what
+    worst = max(diffs, key=diffs.get)
+    if dtype == "float32":
+        assert diffs[worst] <= TOL_F32 * max(1.0, scale), f"{what}: max |diff| {diffs[worst]:.3e} at {worst}"
+        return
+    tol = TOL_BF16_REL * scale
+    diffs = {k: d for k, d in diffs.items() if (k[0].replace("again", ""), k[1]) not in fragile}
+    worst = max(diffs, key=diffs.get)
+    over = [k for k, d in diffs.items() if d > tol]
+    assert len(over) <= max(1, 3 * len(diffs) // 100), \
+        f"{what}: max |diff| {diffs[worst]:.3e} at {worst}, {len(over)} of {len(diffs)} over {tol:.3e}: {sorted(over)[:12]}"
+
+
+def _weights(part, g, dtype, sigma=1.0):
+    w = {s.name: (sigma * torch.randn(s.shape, generator=g) * (1.0 if len(s.shape) == 1 else 1.0 / math.sqrt(s.shape[-1]))
+                  ).bfloat16().float() for s in part.weight_specs()}
+    return w, {k: v.to(DEV, torch.float32 if v.dim() == 1 else dtype) for k, v in w.items()}
+
+
+def _close(got, want, dtype, what, f32=3e-5, bf16=0.03):
+    """float32: every element against the largest of the wanted ones. bfloat16: every row but one in fifty."""
+    scale = want.abs().max().item()
+    d = (got.double() - want).abs().reshape(want.shape[0], -1).amax(dim=1) if want.dim() > 1 else (got.double() - want).abs()
+    if dtype == torch.float32:
+        assert d.max().item() <= f32 * max(1.0, scale), (what, d.max().item(), scale)
+        return
+    over = int((d > bf16 * scale).sum())
+    assert over <= max(1, d.numel() // 50), (what, over, d.max().item(), scale)
+
+
+def _rounded(x, dtype):
+    return x.bfloat16().float() if dtype == torch.bfloat16 else x
+
+
+def _double(w):
+    return {k: v.double() for k, v in w.items()}
+
+
+# ---- mechanisms alone -----------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width,rows", [(70, 33), (256, 5), (1, 3), (100, 1), (2050, 9)])
+def test_norms_around_a_branch_in_one_pass(width, rows, dtype):
+    """``h += norm_b(y)`` and the norm ahead of the next branch over the new rows, one kernel, float32 statistics."""
+    from llm_rs_b200 import ops
+    g = torch.Generator().manual_seed(width)
+    h = 3.0 * torch.randn(rows, width, generator=g)
+    y = _rounded(torch.randn(rows, width, generator=g) * torch.rand(rows, 1, generator=g) * 20.0, dtype)
+    wb, wc = 1.0 + 0.3 * torch.randn(width, generator=g), 1.0 + 0.3 * torch.randn(width, generator=g)
+    want_h = h.double() + P.rms_norm(y.double(), wb.double(), 1e-5)
+    want_x = P.rms_norm(want_h, wc.double(), 1e-5)
+    hd = h.to(DEV)
+    x = ops.outnorm_add_norm(hd, y.to(DEV, dtype), wb.to(DEV), wc.to(DEV), 1e-5, dtype)
+    assert (hd.cpu().double() - want_h).abs().max().item() <= 3e-6 * max(1.0, want_h.abs().max().item())
+    assert x.dtype == dtype
+    _close(x.float().cpu(), want_x, dtype, "normed rows", f32=3e-6, bf16=0.01)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width,rows", [(48, 37), (64, 1), (100, 130), (256, 200)])
+def test_the_stream_re_enters_through_the_embedding(width, rows, dtype):
+    """``h <- W [h ; h0]``: the stream's half and the embedding's half of the matrix are separate products; the
+    embedding's term is made once a step and the new stream is a tensor of its own."""
+    from llm_rs_b200.parts import Runtime
+    from llm_rs_b200.parts.embedding import EmbeddingMix
+    g = torch.Generator().manual_seed(width + rows)
+    part = EmbeddingMix(width, "loop.in")
+    w, wd = _weights(part, g, dtype, 1.0)
+    part.bind(wd, Runtime(torch.device(DEV), dtype, 64))
+    h, h0 = _rounded(2.0 * torch.randn(rows, width, generator=g), dtype), _rounded(torch.randn(rows, width, generator=g), dtype)
+    want = torch.cat([h, h0], dim=-1).double() @ w["loop.in"].double().T
+    ctx = _ctx([rows], [0])
+    hd, h0d = h.to(DEV), h0.to(DEV)
+    entered = part.prepare(h0d, ctx)
+    kept = entered.clone()
+    new = part.forward(hd, None, entered, ctx)
+    assert new.dtype == torch.float32 and new.data_ptr() not in (hd.data_ptr(), entered.data_ptr())
+    assert torch.equal(entered, kept) and torch.equal(hd.cpu(), h)
+    _close(new.cpu(), want, dtype, "re-entry", bf16=0.01)
+    # A branch output that the block before left unadded is added to the stream first.
+    pending = _rounded(torch.randn(rows, width, generator=g), dtype)
+    want2 = torch.cat([h + pending, h0], dim=-1).double() @ w["loop.in"].double().T
+    new2 = part.forward(hd, pending.to(DEV), entered, ctx)
+    _close(new2.cpu(), want2, dtype, "re-entry after an unadded branch", bf16=0.02)
+
+
+def _window_setup(dtype, heads, kv_heads, dk, dv, window, rot_dims, page, n_pages, seed, scale=None, D=56, base=3000.0):
+    from llm_rs_b200.parts import Runtime
+    from llm_rs_b200.parts.scored_attention import ScoredAttention
+    g = torch.Generator().manual_seed(seed)
+    scale = 1.0 / math.sqrt(dk) if scale is None else scale
+    part = ScoredAttention(D, heads, kv_heads, dk, dv, scale=scale, mask="window" if window else "causal",
+                           mask_size=window, qk_norm="head_unit", norm_eps=1e-5, rot_dims=rot_dims, rot_base=base,
+                           gated=True, prefix="m.")
+    w, wd = _weights(part, g, dtype, 1.5)
+    part.bind(wd, Runtime(torch.device(DEV), dtype, 4096))
+    pages = torch.zeros(n_pages, kv_heads, page * (dk + dv), dtype=dtype, device=DEV)
+    planes = [pages[:, :, : page * dk].unflatten(2, (page, dk)), pages[:, :, page * dk:].unflatten(2, (page, dv))]
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dk, "vdim": dv, "scale": scale}
+    if rot_dims:
+        m["rot"] = {"base": base, "dims": rot_dims}
+    if window:
+        m["mask"] = {"size": window}
+    return part, w, planes, m, g, D
+
+
+def _latent_setup(dtype, heads, dn, dr, dv, rank, q_rank, scaling, page, n_pages, seed, scale=0.31, D=56, base=3000.0):
+    from llm_rs_b200.parts import Runtime
+    from llm_rs_b200.parts.latent_attention import LatentAttention
+    g = torch.Generator().manual_seed(seed)
+    sc = dict(zip(("factor", "original", "fast", "slow"), scaling)) if scaling else None
+    part = LatentAttention(D, heads, dn, dr, dv, rank, scale=scale, rot_base=base, rot_dims=dr, norm_eps=1e-5,
+                           gated=False, q_rank=q_rank, rot_pairing="neighbours", rot_scaling=sc, prefix="m.")
+    w, wd = _weights(part, g, dtype, 1.5)
+    part.bind(wd, Runtime(torch.device(DEV), dtype, 4096))
+    pages = torch.zeros(n_pages, 1, page * (rank + dr), dtype=dtype, device=DEV)
+    planes = [pages[:, :, : page * rank].unflatten(2, (page, rank)), pages[:, :, page * rank:].unflatten(2, (page, dr))]
+    rot = {"base": base, "dims": dr}
+    if sc:
+        rot["scaling"] = sc
+    m = {"heads": heads, "dim": dn, "rot_dim": dr, "vdim": dv, "kv_rank": rank, "q_rank": q_rank, "scale": scale, "rot": rot}
+    return part, w, planes, m, g, D
+
+
+def _run_in_cuts(part, planes, seqs, cuts, page, dtype, g, n_pages):
+    """Two requests over scattered pages: a prompt portion each, then portions and single tokens in the same steps."""
+    lens = [s.shape[0] for s in seqs]
+    assert all(sum(c[r] for c in cuts) == n for r, n in enumerate(lens))
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    width = -(-max(lens) // page)
+    table = torch.tensor([perm[:width], perm[width:2 * width]], dtype=torch.int32, device=DEV)
+    cache = SimpleNamespace(planes=planes, block_table=table, page_size=page, owns=True, state={})
+    at, got = [0, 0], [[], []]
+    for cut in cuts:
+        live = [r for r in range(2) if cut[r]]
+        ctx = _ctx([cut[r] for r in live], [at[r] for r in live], planner=part, page_size=page)
+        cache.block_table = table[live].contiguous()
+        x = torch.cat([seqs[r][at[r]: at[r] + cut[r]] for r in live]).to(DEV, dtype)
+        y = part.forward(x, ctx, cache).float().cpu()
+        o = 0
+        for r in live:
+            got[r].append(y[o:o + cut[r]])
+            o += cut[r]
+            at[r] += cut[r]
+    return [torch.cat(rows) for rows in got]
+
+
+CUTS = [(97, 30), (2, 1), (1, 1), (30, 2), (1, 1), (19, 6), (0, 1), (1, 0)]       # 151 and 42 tokens
+
+
+@pytest.mark.parametrize("generic", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv,dk,dv,window,rot,page", [
+    (4, 2, 16, 32, 20, 8, 16), (5, 1, 24, 8, 7, 24, 8), (2, 2, 8, 40, 1, 0, 4), (6, 6, 64, 64, 96, 16, 16),
+    (8, 2, 32, 64, 130, 32, 32), (3, 3, 128, 128, 64, 64, 64), (4, 4, 16, 16, 0, 16, 16), (2, 1, 20, 12, 50, 4, 16),
+    (6, 1, 48, 32, 75, 48, 16), (7, 1, 40, 40, 33, 40, 16), (1, 1, 192, 128, 40, 64, 16), (12, 3, 80, 48, 16, 80, 16)])
+def test_window_attention_mixer_against_plain(dtype, heads, kv, dk, dv, window, rot, page, generic):
+    """The mixer part alone: rotation by halves, every head of q and k divided by its root mean square after it,
+    windows shorter and longer than a page, of one key and none, a sigmoid gate per head on the output; on the
+    tensor cores and on the kernel for any type."""
+    from llm_rs_b200 import ops
+    if generic and dtype == torch.float32:
+        pytest.skip("float32 has one kernel")
+    part, w, planes, m, g, D = _window_setup(dtype, heads, kv, dk, dv, window, rot, page, 128, dk + heads)
+    seqs = [_rounded(torch.randn(n, D, generator=g), dtype) for n in (151, 42)]
+    want = [P.window_attention(s.double(), m, _double(w), "m.", 1e-5) for s in seqs]
+    ops.scored_generic_only(generic)
+    try:
+        got = _run_in_cuts(part, planes, seqs, CUTS, page, dtype, g, 128)
+    finally:
+        ops.scored_generic_only(False)
+    for r in range(2):
+        _close(got[r], want[r], dtype, r)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,dn,dr,dv,rank,q_rank,scaling,page", [
+    (4, 16, 8, 24, 40, 24, (4.0, 64, 8.0, 1.0), 16), (1, 24, 16, 40, 50, 8, None, 8), (5, 8, 32, 8, 100, 64, (8.0, 128, 16.0, 2.0), 4),
+    (8, 32, 32, 32, 128, 96, (2.0, 32, 4.0, 0.5), 16), (3, 64, 64, 16, 300, 40, None, 64), (3, 16, 16, 16, 64, 64, (40.0, 4096, 32.0, 1.0), 16),
+    (6, 32, 16, 32, 96, 160, (2.5, 1024, 24.0, 1.0), 32), (2, 8, 2, 8, 12, 12, (3.0, 8, 2.0, 1.0), 16),
+    (5, 12, 6, 20, 36, 20, (1.5, 40, 3.0, 1.0), 16)])
+def test_latent_attention_mixer_against_plain(dtype, heads, dn, dr, dv, rank, q_rank, scaling, page):
+    """The mixer part alone: queries through a normed latent of their own, one normed latent row and one rotated key
+    part per token in the pages, neighbouring pairs with rescaled frequencies and magnitude, no gate."""
+    part, w, planes, m, g, D = _latent_setup(dtype, heads, dn, dr, dv, rank, q_rank, scaling, page, 128, rank + heads)
+    seqs = [_rounded(torch.randn(n, D, generator=g), dtype) for n in (151, 42)]
+    want = [P.latent_attention(s.double(), m, _double(w), "m.", 1e-5) for s in seqs]
+    got = _run_in_cuts(part, planes, seqs, CUTS, page, dtype, g, 128)
+    for r in range(2):
+        _close(got[r], want[r], dtype, r, bf16=0.04)     # a magnitude above 1 on both sides sharpens the softmax
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("decode", [False, True])
+@pytest.mark.parametrize("window,page,key_at", [(13, 8, 48), (16, 16, 31), (33, 32, 64), (1, 16, 40), (70, 16, 17)])
+def test_window_edges(dtype, decode, window, page, key_at):
+    """One token's row is replaced by a row 25 times larger: its value grows 25-fold (its key keeps unit size). The
+    output must move when that key is the last one inside the window and must stay bit for bit when it is one step
+    outside; for a query inside a prompt's portion and for one decoded alone; keys at a page's first and last row."""
+    part, w, planes, m, g, D = _window_setup(dtype, 2, 1, 16, 12, window, 8, page, 32, 5)
+    n = 160
+    base = torch.randn(n, D, generator=g)
+    other = 25.0 * torch.randn(D, generator=g)
+    outs = {}
+    for name, query_at in (("inside", key_at + window - 1), ("outside", key_at + window)):
+        for planted in (False, True):
+            x = base.clone()
+            if planted:
+                x[key_at] = other
+            x = _rounded(x, dtype)
+            want = P.window_attention(x.double(), m, _double(w), "m.", 1e-5)[query_at]
+            for p in planes:
+                p.zero_()
+            table = torch.arange(31, -1, -1, dtype=torch.int32, device=DEV)[None, : -(-n // page)].contiguous()
+            cache = SimpleNamespace(planes=planes, block_table=table, page_size=page, owns=True, state={})
+            if decode:
+                part.forward(x[:query_at].to(DEV, dtype), _ctx([query_at], [0], planner=part, page_size=page), cache)
+                y = part.forward(x[query_at:query_at + 1].to(DEV, dtype),
+                                 _ctx([1], [query_at], planner=part, page_size=page), cache)[0]
+            else:
+                y = part.forward(x[: query_at + 3].to(DEV, dtype),
+                                 _ctx([query_at + 3], [0], planner=part, page_size=page), cache)[query_at]
+            scale = want.abs().max().item()
+            d = (y.float().cpu().double() - want).abs().max().item()
+            assert d <= (3e-5 * max(1, scale) if dtype == torch.float32 else 0.03 * scale), (name, planted, d, scale)
+            outs[(name, planted)] = y.float().cpu()
+    moved = (outs[("inside", True)] - outs[("inside", False)]).abs().max().item()
+    still = (outs[("outside", True)] - outs[("outside", False)]).abs().max().item()
+    assert moved > 0.02 * outs[("inside", False)].abs().max().item(), moved
+    assert still == 0.0, still
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kind", ["latent", "unmasked"])
+def test_a_far_key_among_hundreds(dtype, kind):
+    """No window: with a score scale several times the usual one the softmax of every query rests on the few keys
+    whose score stands out, and among 900 keys those lie anywhere: hundreds of positions back, at page borders, among
+    the first tokens. A kernel that loses a key far back gives another token's value there. Whole, and with the last
+    60 positions decoded one by one."""
+    n, page = 900, 16
+    if kind == "latent":
+        part, w, planes, m, g, D = _latent_setup(dtype, 2, 16, 8, 12, 24, 16, (4.0, 64, 8.0, 1.0), page, 64, 9, scale=1.4)
+        plain = P.latent_attention
+    else:
+        part, w, planes, m, g, D = _window_setup(dtype, 2, 1, 16, 12, 0, 8, page, 64, 9, scale=1.2)
+        plain = P.window_attention
+    x = _rounded(torch.randn(n, D, generator=torch.Generator().manual_seed(77)), dtype)
+    want = plain(x.double(), m, _double(w), "m.", 1e-5)
+    table = torch.randperm(64, generator=g).to(torch.int32)[None, : -(-n // page)].contiguous().to(DEV)
+    cache = SimpleNamespace(planes=planes, block_table=table, page_size=page, owns=True, state={})
+    ctx = lambda k, at: _ctx([k], [at], planner=part, page_size=page)
+    whole = part.forward(x.to(DEV, dtype), ctx(n, 0), cache).float().cpu()
+    _close(whole, want, dtype, "whole", bf16=0.06)
+    for p in planes:
+        p.zero_()
+    head = n - 60
+    rows = [part.forward(x[:head].to(DEV, dtype), ctx(head, 0), cache).float().cpu()]
+    rows += [part.forward(x[i:i + 1].to(DEV, dtype), ctx(1, i), cache).float().cpu() for i in range(head, n)]
+    _close(torch.cat(rows), want, dtype, "tail decoded", bf16=0.06)
+
+
+def test_router_chooses_by_corrected_score_and_weighs_by_score():
+    """Hand-made logits: the scores are a softmax over ALL outputs; the correction steers the choice only; the weights
+    are the scores themselves and do not sum to one; the last outputs are identity experts, reported as one group."""
+    from llm_rs_b200 import ops
+    z = torch.tensor([[0.0, 5.0, 1.0, 4.0, -2.0, 3.0], [1.0, 1.0, 1.0, 1.0, 1.0, 1.0], [2.0, 0.0, 0.0, 0.0, 0.0, 1.9]],
+                     device=DEV)
+    s = torch.softmax(z.double().cpu(), dim=-1)
+    none = torch.zeros(6, device=DEV)
+    e, p = ops.moe_route_biased(z, none, 6, 6, 3)
+    assert e.view(3, 3).tolist() == [[1, 3, 5], [0, 1, 2], [0, 5, 1]]      # falling score; the lower expert among equals
+    assert (p.view(3, 3).cpu().double() - torch.gather(s, 1, e.view(3, 3).cpu().long())).abs().max().item() < 1e-6
+    assert abs(float(p.view(3, 3)[1].sum()) - 0.5) < 1e-6                   # not renormalised
+    # A correction of +1 lifts expert 4 above all others (scores are below 1); its weight is still its score.
+    lift = torch.tensor([0.0, 0.0, 0.0, 0.0, 1.0, 0.0], device=DEV)
+    e, p = ops.moe_route_biased(z, lift, 6, 6, 2)
+    assert e.view(3, 2).tolist() == [[4, 1], [4, 0], [4, 0]]
+    assert (p.view(3, 2)[:, 0].cpu().double() - s[:, 4]).abs().max().item() < 1e-6
+    # The last two outputs are identity experts: both are group 4; each keeps its own score.
+    e, p = ops.moe_route_biased(z, none, 6, 4, 3)
+    assert e.view(3, 3).tolist() == [[1, 3, 4], [0, 1, 2], [0, 4, 1]]
+    assert abs(float(p.view(3, 3)[2, 1]) - float(s[2, 5])) < 1e-6
+    # Columns beyond the router's outputs (a product padded to a wider row) are no experts.
+    wide = torch.cat([z, torch.full((3, 2), 50.0, device=DEV)], dim=1)
+    e2, p2 = ops.moe_route_biased(wide[:, :6], none, 6, 4, 3)
+    assert torch.equal(e2, e) and torch.equal(p2, p)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("experts,top,identity,n_tokens", [
+    (4, 2, 1, 50), (3, 3, 0, 7), (1, 1, 1, 5), (37, 4, 3, 300), (8, 1, 0, 1), (12, 3, 2, 260), (200, 6, 0, 40),
+    (2, 5, 3, 33), (5, 5, 0, 64), (16, 4, 4, 129)])
+def test_routed_experts_against_plain(dtype, experts, top, identity, n_tokens):
+    """Scores over all experts, choice by score plus correction, identity experts (also more of them than real ones,
+    every output chosen), plain SiLU unit."""
+    from llm_rs_b200.parts import Runtime
+    from llm_rs_b200.parts.moe import MixtureOfExperts
+    g = torch.Generator().manual_seed(experts * 10 + top)
+    D, F = 48, 40
+    part = MixtureOfExperts(D, F, experts, top, router="softmax_bias", n_identity=identity, limit=None, alpha=1.0,
+                            up_shift=0.0, prefix="f.")
+    w, wd = _weights(part, g, dtype, 1.5)
+    w["f.router"] = (3.0 * w["f.router"]).bfloat16().float()      # scores well apart: no pick rests on a close call
+    w["f.correction"] = (0.2 * w["f.correction"]).bfloat16().float()
+    wd["f.router"], wd["f.correction"] = w["f.router"].to(DEV, dtype), w["f.correction"].to(DEV)
+    part.bind(wd, Runtime(torch.device(DEV), dtype, 64))
+    x = _rounded(torch.randn(n_tokens, D, generator=g), dtype)
+    f = {"kind": "moe", "expert": {"ff": F}, "router": {"experts": experts, "top": top, "identity": identity}}
+    want = P.routed_experts(x.double(), f, _double(w), "f.")
+    got = part.forward(x.to(DEV, dtype), SimpleNamespace(token_ids=None)).float().cpu()
+    _close(got, want, dtype, "experts")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_dense_feed_forward_against_plain(dtype):
+    from llm_rs_b200.parts import Runtime
+    from llm_rs_b200.parts.mlp import SwiGLU
+    g = torch.Generator().manual_seed(3)
+    part = SwiGLU(40, 72, names={"gate": "gate", "up": "up", "down": "down"}, suffix="", prefix="f.")
+    w, wd = _weights(part, g, dtype, 1.5)
+    part.bind(wd, Runtime(torch.device(DEV), dtype, 64))
+    x = _rounded(torch.randn(33, 40, generator=g), dtype)
+    want = P.gated_unit(x.double(), _double(w), "f.")
+    _close(part.forward(x.to(DEV, dtype), None).float().cpu(), want, dtype, "dense")
+
+
+# ---- whole models -----------------------------------------------------------------------------------
+def _steps(mode, reqs):
+    if mode == "tail":
+        return RU.tail_one_by_one(reqs, tail=70)      # longer than every window but C's widest
+    if mode == "portions":
+        return RU.portions(reqs, sizes=(1, 1, 2, 7, 2, 13, 5, 2, 31, 3, 17, 2, 64))
+    return {"whole": RU.whole, "mixed": RU.mixed}[mode](reqs)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("name", list(POZELIX))
+def test_replay_matches_plain(models, name, mode, dtype):
+    from llm_rs_b200.engine import ModelRunner
+    path, cfg, w, reqs, ref = models[name]
+    steps = _steps(mode, reqs)
+    runner = ModelRunner.from_model_dir(path, dtype=getattr(torch, dtype), max_tokens=RU.live_token_peak(steps),
+                                        page_size=POZELIX[name][3], max_requests=4)
+    free_before = [runner.manager.free_pages(g) for g in range(len(runner.manager.groups))]
+    got = RU.run_steps(runner, steps)
+    assert [runner.manager.free_pages(g) for g in range(len(runner.manager.groups))] == free_before, "pages were lost"
+    runner.check_kernels()
+    assert len(got) == sum(len(t) for t in reqs.values())
+    _assert_logits(got, ref, dtype, f"{name} {mode} {dtype}", FRAGILE[name])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", [21, 22])
+@pytest.mark.parametrize("name", list(POZELIX))
+def test_mixed_replay_with_other_cuts_and_pages_used_again(models, name, seed, dtype):
+    """Mixed batches with other seeds and portion sizes, two or three live requests, the requests twice over, so that
+    every page serves several requests."""
+    from llm_rs_b200.engine import ModelRunner
+    path, cfg, w, reqs, ref = models[name]
+    rng = np.random.default_rng(seed)
+    sizes = tuple(int(x) for x in rng.choice([2, 3, 7, 16, 31, 33, 64, 65, 129], size=5, replace=False))
+    twice = {**reqs, **{r + "again": t for r, t in reqs.items()}}
+    steps = RU.mixed(twice, seed=seed, max_live=2 + seed % 2, decode_tail=5 + seed % 7, sizes=sizes)
+    runner = ModelRunner.from_model_dir(path, dtype=getattr(torch, dtype), max_tokens=RU.live_token_peak(steps),
+                                        page_size=POZELIX[name][3], max_requests=3)
+    got = RU.run_steps(runner, steps)
+    assert len(got) == 2 * sum(len(t) for t in reqs.values())
+    _assert_logits(got, ref, dtype, f"{name} seed {seed} {dtype}", FRAGILE[name])
+
+
+def test_long_decoding_beyond_the_pool(models):
+    """A request of 600 tokens through model E (windows only, a loop of one layer that runs four times) with pages for
+    192 tokens: the windows give pages back as they pass. 60 tokens as portions, the other 540 decoded one by one."""
+    from llm_rs_b200.engine import ModelRunner
+    path, cfg, w, reqs, ref = models["E"]
+    toks = np.random.default_rng(5).integers(0, cfg["vocab"], 600).tolist()
+    want = P.forward(toks, cfg, w).numpy()
+    runner = ModelRunner.from_model_dir(path, dtype=torch.float32, max_tokens=192, page_size=32, max_requests=2)
+    steps = [{"entries": [{"id": "long", "tokens": toks[a:a + 30], "want": list(range(30))}], "end": []} for a in (0, 30)]
+    steps += [{"entries": [{"id": "long", "tokens": [t], "want": [0]}], "end": []} for t in toks[60:]]
+    got = RU.run_steps(runner, steps)
+    worst, where, n = RU.max_diff(got, {"long": want})
+    assert n == 600 and worst <= TOL_F32 * max(1.0, float(np.abs(want).max())), (worst, where)
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(POZELIX))
+def test_greedy_generation_through_the_engine(models, name, dtype, graphs):
+    """Prompts of unequal length through ``Engine.generate``: scheduler, prompt portions, decoding (captured in CUDA
+    graphs or not), the device sampler's argmax. float32 gives the plain implementation's tokens; bfloat16 may choose
+    another token only where the plain logits of the two are closer than its rounding."""
+    from llm_rs_b200.engine import Engine, EngineConfig
+    from llm_rs_b200.sampling import SamplingParams
+    path, cfg, w, reqs, ref = models[name]
+    prompts = [reqs[r][:n] for r, n in zip(list(reqs)[1:4], (9, 33, 20))]
+    engine = Engine(EngineConfig(model_path=path, block_pool_size=64, page_size=POZELIX[name][3], dtype=dtype,
+                                 max_requests=4, cuda_graphs=graphs, prefill_chunk=16, max_tokens_per_step=24))
+    got = engine.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=12, ignore_eos=True))
+    for prompt, new in zip(prompts, got):
+        assert len(new) == 12
+        toks = list(prompt)
+        for t in new:
+            row = P.forward(toks, cfg, w)[-1]
+            gap = float(row.max() - row[t])
+            assert gap <= (1e-4 if dtype == "float32" else 0.06) * float(row.abs().max()), (name, gap)
+            toks.append(t)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_program_on_a_pozelix_folder(models, tmp_path, dtype):
+    """bin/trace_run picks the design by config.json and replays a mixed trace."""
+    path, cfg, w, reqs, ref = models["B"]
+    steps = RU.want_only(RU.mixed(reqs, seed=9), {r: set(range(0, len(t), 3)) | {len(t) - 1} for r, t in reqs.items()})
+    out_dir = tmp_path / "out"
+    lines = [json.dumps({"step": i, **st}) for i, st in enumerate(steps)]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    proc = subprocess.run(
+        [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", path, "--dtype", dtype, "--out", str(out_dir),
+         "--max-tokens", str(RU.live_token_peak(steps)), "--max-requests", "4", "--page-size", "8"],
+        input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split("\n")[:len(steps)] == [f"done {i}" for i in range(len(steps))]
+    at, got, V = {}, {}, cfg["vocab"]
+    for i, st in enumerate(steps):
+        n_want = sum(len(e["want"]) for e in st["entries"])
+        if not n_want:
+            assert not (out_dir / f"{i}.f32").exists()
+        else:
+            data = np.fromfile(out_dir / f"{i}.f32", dtype="<f4").reshape(-1, V)
+            assert data.shape[0] == n_want
+        k = 0
+        for e in st["entries"]:
+            base = at.get(e["id"], 0)
+            for wnt in e["want"]:
+                got[(e["id"], base + wnt)] = data[k]
+                k += 1
+            at[e["id"]] = base + len(e["tokens"])
+    _assert_logits(got, ref, dtype, f"trace program {dtype}", FRAGILE["B"])
+
+
+def test_command_line_writes_and_runs_a_pozelix_folder(tmp_path):
+    """``random_model`` from a config.json of the design, then ``run_model`` with sampling switched off: the registry,
+    the loader, the engine and the sampler through the command line; the tokens are the plain implementation's."""
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(POZELIX["A"][0]))
+    out = tmp_path / "model"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    run = lambda *a: subprocess.run([sys.executable, "-m", "llm_rs_b200.cli", *a], cwd=root, capture_output=True,
+                                    text=True, timeout=600)
+    made = run("random_model", "--config", str(cfg_path), "--out", str(out), "--seed", "3", "--sigma", "0.15",
+               "--norm-jitter", "0.2")
+    assert made.returncode == 0, made.stderr[-2000:]
+    prompt = [5, 17, 3, 9, 200, 41, 7, 7, 150]
+    done = run("run_model", "--model-path", str(out), "--prompt-ids", ",".join(map(str, prompt)), "--dtype", "float32",
+               "--max-new-tokens", "10", "--ignore-eos", "--page-size", "16", "--block-pool-size", "32")
+    assert done.returncode == 0, done.stderr[-2000:]
+    lines = dict(l.split(":", 1) for l in done.stdout.splitlines() if ":" in l)
+    got = [int(t) for t in lines["Generated token ids"].split(",")]
+    cfg, w = P.load_model_dir(str(out))
+    seq = list(prompt)
+    for tok in got:
+        row = P.forward(seq, cfg, w)[-1]
+        assert float(row.max() - row[tok]) <= 1e-4 * float(row.abs().max())
+        seq.append(tok)
+    assert len(got) == 10
