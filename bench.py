@@ -429,7 +429,8 @@ def main():
                     "through the engine on the layer sizes of Qwen3-14B / Qwen3-32B. rusadra: prefill and decode of the "
                     "Rusadra design beside Qwen3 at equal width, depth, vocabulary and active feed-forward width, with "
                     "every kernel class's fraction of the device's peaks. pusazen: the same for the Pusazen design "
-                    "beside Rusadra at equal width, depth, vocabulary, experts and expert width")
+                    "beside Rusadra at equal width, depth, vocabulary, experts and expert width. pozelix: the same "
+                    "for the Pozelix design beside Rusadra and Pusazen")
     ap.add_argument("--pool-tokens", type=int, default=0, help="size of the cache pool of a --workload run in "
                     "tokens (default: what holds every request whole); smaller makes the scheduler preempt")
     args = ap.parse_args()

@@ -13,6 +13,9 @@
 //                     softmax in float32 kept online per warp and merged through shared memory; the result is the
 //                     attention-weighted latent times sigmoid(gate) of the head (the gate is a scalar per head, so it
 //                     commutes with the value up-projection that follows).
+//   steps of few tokens  (decoding) cut every token's keys into runs that separate blocks take and a merge kernel
+//                     joins: in bfloat16 on the tensor cores, a block per token with all its heads (up to 32) as the
+//                     rows of the products (`latent_decode_mma_kernel`), else on CUDA cores with a lane per key.
 #include "common.cuh"
 #include "mma_util.cuh"
 
@@ -455,6 +458,268 @@ static bool try_latent_decode(int* rc, dim3 grid, cudaStream_t stream, const voi
   return true;
 }
 
+// ---------------------------------------------------------------------------------
+// Steps of few tokens in bfloat16 on the tensor cores (mma.sync m16n8k16). A block takes ONE token and up to 16 * MT of
+// its heads as the rows of the product and a run of `split_keys` keys (counted from the first visible key, rounded
+// down to a multiple of 16), 16 keys at a time: a key's cached row [latent | rotated part] comes into shared memory
+// once for all the heads (16-byte asynchronous copies, three buffers) and is the key operand (all rank + rot columns)
+// and the value operand (the latent columns). The four warps split the k range of the score product, add their partial
+// scores through shared memory, keep the same online softmax each (float32; the weights are rounded to bfloat16 as
+// the value product's operand, as in the prompt kernel) and own a quarter of the latent columns each. Every block
+// leaves its unnormalised sums, maximum and denominator in `partial` for the merge kernel. Needs rank % 64 == 0,
+// rot % 16 == 0, pages of a multiple of 16 keys and split_keys % 16 == 0.
+// ---------------------------------------------------------------------------------
+constexpr int LDM_STAGES = 3;
+static int g_latent_decode_mma = 1;
+LLMRS_API void llmrs_latent_decode_mma(int on) { g_latent_decode_mma = on; }
+
+template <int MT, int NTV>      // NTV: 8-column pieces of the output per warp, at most (rank / 32)
+__global__ void __launch_bounds__(128)
+latent_decode_mma_kernel(const __nv_bfloat16* __restrict__ qa, long long qa_token, long long qa_head,
+                         const __nv_bfloat16* __restrict__ q, long long q_stride, int q_rot_at, int q_head_width,
+                         const __nv_bfloat16* __restrict__ cache, const int* __restrict__ table, int table_width,
+                         const int* __restrict__ positions, const int* __restrict__ token_req, int n_heads, int rank,
+                         int dr, int page_size, int window, float scale, int split_keys, float* __restrict__ partial) {
+  typedef __nv_bfloat16 bf16;
+  constexpr int ROWS = 16 * MT;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int KD = rank + dr, LD = KD + 8;
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                          // [ROWS][LD]
+  bf16* Ks = Qs + ROWS * LD;                                             // [stages][16][LD]
+  float* Sp = reinterpret_cast<float*>(Ks + LDM_STAGES * 16 * LD);       // [4][ROWS][17]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int tok = blockIdx.x, h0 = blockIdx.y * ROWS, z = blockIdx.z, n_splits = gridDim.z;
+  const int pos = positions[tok];
+  const int* tab = table + (size_t)token_req[tok] * table_width;
+
+  // Row r of the block is head h0 + r. Eight threads copy a row.
+  for (int r = tid >> 3; r < ROWS; r += 16) {
+    const int h = h0 + r;
+    const bool there = h < n_heads;
+    const bf16* qa_row = qa + (size_t)tok * qa_token + (size_t)(there ? h : 0) * qa_head;
+    const bf16* qr_row = q + (size_t)tok * q_stride + (size_t)(there ? h : 0) * q_head_width + q_rot_at;
+    bf16* dst = Qs + r * LD;
+    for (int c = tid & 7; c < rank; c += 8) dst[c] = there ? qa_row[c] : __float2bfloat16_rn(0.f);
+    for (int c = tid & 7; c < dr; c += 8) dst[rank + c] = there ? qr_row[c] : __float2bfloat16_rn(0.f);
+  }
+  bool row_there[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) row_there[mt][hf] = h0 + 16 * mt + g + 8 * hf < n_heads;
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int j_first = (lo / 16) * 16 + z * split_keys;
+  const int j_end = min(pos, j_first + split_keys - 1);
+  const int n_tiles = j_end >= j_first ? (j_end - j_first) / 16 + 1 : 0;
+  const size_t page_elems = (size_t)page_size * KD;
+  const int chunks = KD / 8, c_chunks = rank / 8;
+  auto load_tile = [&](int stage, int j0) {
+    const int page = tab[j0 / page_size], slot0 = j0 % page_size;
+    const bf16* base = cache + (size_t)(page < 0 ? 0 : page) * page_elems;
+    bf16* dst = Ks + (size_t)stage * 16 * LD;
+    const int key = tid >> 3;
+    const bool in = page >= 0 && j0 + key <= j_end;           // later keys: zeros
+    const bf16* c_src = base + (size_t)(slot0 + key) * rank;
+    const bf16* r_src = base + (size_t)page_size * rank + (size_t)(slot0 + key) * dr;
+    bf16* row = dst + key * LD;
+    for (int ch = tid & 7; ch < c_chunks; ch += 8) cp_async_16(row + ch * 8, c_src + ch * 8, in ? 16 : 0);
+    for (int ch = tid & 7; ch < chunks - c_chunks; ch += 8) cp_async_16(row + rank + ch * 8, r_src + ch * 8, in ? 16 : 0);
+  };
+
+  float acc[MT][NTV][4], m[MT][2], l[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    m[mt][0] = m[mt][1] = -INFINITY;
+    l[mt][0] = l[mt][1] = 0.f;
+#pragma unroll
+    for (int i = 0; i < NTV; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[mt][i][e] = 0.f;
+  }
+  const int ntv = rank / 32, cw0 = warp * (rank / 4), k_steps = KD / 16;
+
+  // One group of copies per tile, also where there is no tile to copy, so that the count of groups in flight is fixed.
+#pragma unroll
+  for (int s = 0; s < LDM_STAGES - 1; ++s) {
+    if (s < n_tiles) load_tile(s, j_first + 16 * s);
+    cp_async_commit();
+  }
+  for (int kt = 0; kt < n_tiles; ++kt) {
+    const int stage = kt % LDM_STAGES, j0 = j_first + 16 * kt;
+    if (kt + LDM_STAGES - 1 < n_tiles) load_tile((kt + LDM_STAGES - 1) % LDM_STAGES, j0 + 16 * (LDM_STAGES - 1));
+    cp_async_commit();
+    cp_async_wait<LDM_STAGES - 1>();
+    __syncthreads();
+    const bf16* K = Ks + (size_t)stage * 16 * LD;
+    float sp[MT][2][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sp[mt][nt][e] = 0.f;
+    for (int ks = warp; ks < k_steps; ks += 4) {
+      uint32_t b[2][2];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        b[nt][0] = *reinterpret_cast<const uint32_t*>(K + (nt * 8 + g) * LD + ks * 16 + 2 * t);
+        b[nt][1] = *reinterpret_cast<const uint32_t*>(K + (nt * 8 + g) * LD + ks * 16 + 2 * t + 8);
+      }
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const bf16* Q = Qs + (16 * mt) * LD + ks * 16 + 2 * t;
+        uint32_t a[4];
+        a[0] = *reinterpret_cast<const uint32_t*>(Q + g * LD);
+        a[1] = *reinterpret_cast<const uint32_t*>(Q + (g + 8) * LD);
+        a[2] = *reinterpret_cast<const uint32_t*>(Q + g * LD + 8);
+        a[3] = *reinterpret_cast<const uint32_t*>(Q + (g + 8) * LD + 8);
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) mma_bf16_16816(sp[mt][nt], a, b[nt][0], b[nt][1]);
+      }
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          Sp[(warp * ROWS + 16 * mt + g + 8 * (e >> 1)) * 17 + nt * 8 + 2 * t + (e & 1)] = sp[mt][nt][e];
+    __syncthreads();
+    uint32_t pf[MT][4];
+    float corr[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      float p[2][4];
+      float row_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int hf = e >> 1, col = nt * 8 + 2 * t + (e & 1), j = j0 + col;
+          float sv = 0.f;
+#pragma unroll
+          for (int w = 0; w < 4; ++w) sv += Sp[(w * ROWS + 16 * mt + g + 8 * hf) * 17 + col];
+          const bool seen = row_there[mt][hf] && j <= j_end && j >= lo;
+          sv = seen ? sv * scale : -INFINITY;
+          p[nt][e] = sv;
+          row_max[hf] = fmaxf(row_max[hf], sv);
+        }
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        row_max[hf] = fmaxf(row_max[hf], __shfl_xor_sync(0xffffffffu, row_max[hf], 1));
+        row_max[hf] = fmaxf(row_max[hf], __shfl_xor_sync(0xffffffffu, row_max[hf], 2));
+        const float m_new = fmaxf(m[mt][hf], row_max[hf]);
+        corr[mt][hf] = m_new == -INFINITY ? 1.f : expf(m[mt][hf] - m_new);
+        float sum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float v = m_new == -INFINITY ? 0.f : expf(p[nt][2 * hf + e] - m_new);
+            p[nt][2 * hf + e] = v;
+            sum += v;
+          }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l[mt][hf] = l[mt][hf] * corr[mt][hf] + sum;
+        m[mt][hf] = m_new;
+      }
+      pf[mt][0] = pack_bf16(p[0][0], p[0][1]);
+      pf[mt][1] = pack_bf16(p[0][2], p[0][3]);
+      pf[mt][2] = pack_bf16(p[1][0], p[1][1]);
+      pf[mt][3] = pack_bf16(p[1][2], p[1][3]);
+    }
+    const int jm = lane >> 3;
+#pragma unroll
+    for (int nc = 0; nc < NTV / 2; ++nc) {
+      if (2 * nc >= ntv) break;
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, K + ((jm & 1) * 8 + (lane & 7)) * LD + cw0 + (2 * nc + (jm >> 1)) * 8);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc[mt][2 * nc][e] *= corr[mt][e >> 1];
+          acc[mt][2 * nc + 1][e] *= corr[mt][e >> 1];
+        }
+        mma_bf16_16816(acc[mt][2 * nc], pf[mt], b[0], b[1]);
+        mma_bf16_16816(acc[mt][2 * nc + 1], pf[mt], b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      if (!row_there[mt][hf]) continue;
+      const int h = h0 + 16 * mt + g + 8 * hf;
+      float* p = partial + (((size_t)tok * n_heads + h) * n_splits + z) * (rank + 2);
+#pragma unroll
+      for (int nt = 0; nt < NTV; ++nt) {
+        if (nt >= ntv) break;
+        p[cw0 + nt * 8 + 2 * t] = acc[mt][nt][2 * hf];
+        p[cw0 + nt * 8 + 2 * t + 1] = acc[mt][nt][2 * hf + 1];
+      }
+      if (warp == 0 && t == 0) p[rank] = m[mt][hf], p[rank + 1] = l[mt][hf];
+    }
+}
+
+template <int MT, int NTV>
+static int launch_latent_decode_mma(dim3 grid, size_t smem, cudaStream_t stream, const void* qa, long long qa_token,
+                                    long long qa_head, const void* q, long long q_stride, int q_rot_at,
+                                    int q_head_width, const void* cache, const int* table, int table_width,
+                                    const int* positions, const int* token_req, int n_heads, int rank, int dr,
+                                    int page_size, int window, float scale, int split_keys, float* partial) {
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(latent_decode_mma_kernel<MT, NTV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return llmrs_fail("latent_attention (few tokens, tensor cores): shared memory %zu: %s", smem,
+                                            cudaGetErrorString(e));
+    configured = smem;
+  }
+  typedef __nv_bfloat16 bf16;
+  latent_decode_mma_kernel<MT, NTV><<<grid, 128, smem, stream>>>(
+      (const bf16*)qa, qa_token, qa_head, (const bf16*)q, q_stride, q_rot_at, q_head_width, (const bf16*)cache, table,
+      table_width, positions, token_req, n_heads, rank, dr, page_size, window, scale, split_keys, partial);
+  return llmrs_launch_status("latent_attention (few tokens, tensor cores)");
+}
+
+// Heads per block of the kernel above for a number of heads.
+LLMRS_API int llmrs_latent_decode_mma_heads(int n_heads) { return n_heads > 16 ? 32 : 16; }
+
+// Launches the tensor-core kernel when the sizes allow it (returns false otherwise, having launched nothing).
+static bool try_latent_decode_mma(int* rc, int n_tokens, int n_splits, cudaStream_t stream, const void* qa,
+                                  long long qa_token, long long qa_head, const void* q, long long q_stride,
+                                  int q_rot_at, int q_head_width, const void* cache, const int* table,
+                                  int table_width, const int* positions, const int* token_req, int n_heads, int rank,
+                                  int dr, int page_size, int window, float scale, int split_keys, float* partial) {
+  if (!g_latent_decode_mma || rank % 64 || rank > 512 || dr % 16 || page_size % 16 || split_keys % 16 ||
+      ((uintptr_t)cache & 15))
+    return false;
+  const int rows = llmrs_latent_decode_mma_heads(n_heads), LD = rank + dr + 8;
+  const size_t smem = (size_t)(rows + LDM_STAGES * 16) * LD * sizeof(__nv_bfloat16) + (size_t)4 * rows * 17 * sizeof(float);
+  dim3 grid(n_tokens, (n_heads + rows - 1) / rows, n_splits);
+  if (grid.y > 65535) return false;
+#define LLMRS_LDM_ARGS                                                                                             \
+  grid, smem, stream, qa, qa_token, qa_head, q, q_stride, q_rot_at, q_head_width, cache, table, table_width,       \
+      positions, token_req, n_heads, rank, dr, page_size, window, scale, split_keys, partial
+  const int ntv = rank / 32;
+  if (rows == 32) {
+    if (ntv <= 4) *rc = launch_latent_decode_mma<2, 4>(LLMRS_LDM_ARGS);
+    else if (ntv <= 8) *rc = launch_latent_decode_mma<2, 8>(LLMRS_LDM_ARGS);
+    else *rc = launch_latent_decode_mma<2, 16>(LLMRS_LDM_ARGS);
+  } else {
+    if (ntv <= 4) *rc = launch_latent_decode_mma<1, 4>(LLMRS_LDM_ARGS);
+    else if (ntv <= 8) *rc = launch_latent_decode_mma<1, 8>(LLMRS_LDM_ARGS);
+    else *rc = launch_latent_decode_mma<1, 16>(LLMRS_LDM_ARGS);
+  }
+#undef LLMRS_LDM_ARGS
+  return true;
+}
+
 // qa: folded queries [tokens, heads, rank] with strides; q: the projected queries, head h's rotated part at
 // q + t * q_stride + h * q_head_width + q_rot_at; gate: raw gate values [tokens, heads] (row stride given);
 // out: [tokens, heads, rank] with strides. n_splits > 1: every (token, head group) is cut into n_splits blocks of
@@ -486,7 +751,12 @@ LLMRS_API int llmrs_latent_attention(const void* qa, long long qa_token, long lo
 #define LLMRS_LD_ARGS                                                                                              \
   &rc, grid, stream, qa, qa_token, qa_head, q, q_stride, q_rot_at, q_head_width, cache, table, table_width,        \
       positions, token_req, n_heads, rank, dr, page_size, window, scale, split_keys, partial
-    if (dtype == LLMRS_F32) done = try_latent_decode<float>(LLMRS_LD_ARGS);
+    if (dtype == LLMRS_BF16)
+      done = try_latent_decode_mma(&rc, n_tokens, n_splits, stream, qa, qa_token, qa_head, q, q_stride, q_rot_at,
+                                   q_head_width, cache, table, table_width, positions, token_req, n_heads, rank, dr,
+                                   page_size, window, scale, split_keys, partial);
+    if (done) {
+    } else if (dtype == LLMRS_F32) done = try_latent_decode<float>(LLMRS_LD_ARGS);
     else if (dtype == LLMRS_BF16) done = try_latent_decode<__nv_bfloat16>(LLMRS_LD_ARGS);
 #undef LLMRS_LD_ARGS
     if (done) {

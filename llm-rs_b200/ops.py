@@ -906,17 +906,47 @@ def latent_prepare(q: torch.Tensor, dkv: Optional[torch.Tensor], latent_norm_w, 
 LATENT_FEW_TOKENS = 64      # steps of at most this many tokens take the latent attention kernel laid out for latency
 
 
-def latent_attention_splits(n_tokens: int, n_heads: int, span: int, sms: int):
+def latent_attention_splits(n_tokens: int, n_heads: int, span: int, sms: int, mma: bool = False):
     """(splits, keys per split) for a step of ``n_tokens`` whose tokens see at most ``span`` keys: few tokens (decoding)
-    cut their keys so that the blocks fill the device about four times, at 64 keys or more each (measured at 16 heads
-    over a latent of 512 and 4,096 keys: 8 tokens 165 us with 9 runs of keys, 133 us with 18; 64 tokens 1,194 us
-    uncut, 812 us in 2 runs; more runs than that lose again); many tokens are not cut."""
-    blocks = n_tokens * -(-n_heads // (4 if n_heads >= 4 else 1))
-    splits = min(max(1, (4 * sms) // max(blocks, 1)), max(1, span // 64))
+    cut their keys over several blocks; many tokens are not cut. The CUDA-core kernel (a block per token and four
+    heads) fills the device about four times, at 64 keys or more each (measured at 16 heads over a latent of 512 and
+    4,096 keys: 8 tokens 165 us with 9 runs of keys, 133 us with 18; 64 tokens 1,194 us uncut, 812 us in 2 runs; more
+    runs than that lose again). The tensor-core kernel (``mma``: a block per token and up to 32 heads) fills it about
+    twice, at 128 keys or more each. Runs are multiples of 16 keys and cover ``span`` + 15 (a run starts at a multiple
+    of 16 at or below the first visible key)."""
+    span += 15
+    if mma:
+        blocks = n_tokens * -(-n_heads // latent_decode_mma_heads(n_heads))
+        splits = min(max(1, (2 * sms) // max(blocks, 1)), max(1, span // 128))
+    else:
+        blocks = n_tokens * -(-n_heads // (4 if n_heads >= 4 else 1))
+        splits = min(max(1, (4 * sms) // max(blocks, 1)), max(1, span // 64))
     if splits <= 1:
         return 1, 0
     keys = -(-(-(-span // splits)) // 16) * 16
     return -(-span // keys), keys
+
+
+_latent_decode_mma = os.environ.get("LLMRS_LATENT_DECODE_MMA", "1") != "0"
+_latent_decode_mma_sent = None
+
+
+def latent_decode_mma(on: bool) -> None:
+    """Steps of few tokens in bfloat16 take the tensor-core kernel of latent attention where the sizes fit (default,
+    ``LLMRS_LATENT_DECODE_MMA=0`` at import switches it off), or always the CUDA-core kernel."""
+    global _latent_decode_mma
+    _latent_decode_mma = bool(on)
+
+
+def latent_decode_mma_heads(n_heads: int) -> int:
+    """Heads per block of the tensor-core kernel for steps of few tokens."""
+    return 32 if n_heads > 16 else 16
+
+
+def latent_decode_takes_mma(dtype: torch.dtype, rank: int, dr: int, page_size: int) -> bool:
+    """Whether a step of few tokens with these sizes runs on the tensor cores (the kernel's own conditions)."""
+    return (_latent_decode_mma and dtype == torch.bfloat16 and rank % 64 == 0 and rank <= 512 and dr % 16 == 0
+            and page_size % 16 == 0)
 
 
 def latent_attention(qa: torch.Tensor, q: torch.Tensor, gate: torch.Tensor, cache: torch.Tensor, table, ctx,
@@ -941,6 +971,10 @@ def latent_attention(qa: torch.Tensor, q: torch.Tensor, gate: torch.Tensor, cach
         n_floats = qa.size(0) * n_heads * splits * (rank + 2)
         partial = ctx.scratch("latent_attention", n_floats) if hasattr(ctx, "scratch") else torch.empty(
             (n_floats,), dtype=torch.float32, device=qa.device)
+    global _latent_decode_mma_sent
+    if _latent_decode_mma_sent != _latent_decode_mma:
+        _lib().llmrs_latent_decode_mma(int(_latent_decode_mma))
+        _latent_decode_mma_sent = _latent_decode_mma
     _check(_lib().llmrs_latent_attention(
         _ptr(qa), _LL(qs), _LL(qh), _ptr(q), _LL(_row_stride(q, "q")), dn, dn + dr, _ptr(gate),
         _LL(_row_stride(gate, "gate")), _ptr(cache), dtype_code(qa.dtype), _ptr(table), table.size(1),

@@ -230,7 +230,9 @@ class LatentAttention(Mixer):
         # Steps of few tokens cut the visible keys over several blocks. The span is what the step's shape implies (the
         # window, else what the block table can hold), not the requests' lengths: a captured step replays it.
         span = self.window if self.window > 0 else cache.block_table.size(1) * cache.page_size
-        splits, split_keys = ops.latent_attention_splits(T, nh, span, ops.sm_count(proj.device))
+        splits, split_keys = ops.latent_attention_splits(
+            T, nh, span, ops.sm_count(proj.device),
+            mma=T <= ops.LATENT_FEW_TOKENS and ops.latent_decode_takes_mma(proj.dtype, rank, dr, cache.page_size))
         ops.latent_attention(qa, q, gate, pages, cache.block_table, ctx, lat, nh, dn, dr, rank, cache.page_size,
                              self.window, self.scale, splits=splits, split_keys=split_keys)
         out = torch.empty((T, nh, self.vdim), dtype=proj.dtype, device=proj.device)

@@ -278,14 +278,24 @@ def test_window_attention_mixer_against_plain(dtype, heads, kv, dk, dv, window, 
     (4, 16, 8, 24, 40, 24, (4.0, 64, 8.0, 1.0), 16), (1, 24, 16, 40, 50, 8, None, 8), (5, 8, 32, 8, 100, 64, (8.0, 128, 16.0, 2.0), 4),
     (8, 32, 32, 32, 128, 96, (2.0, 32, 4.0, 0.5), 16), (3, 64, 64, 16, 300, 40, None, 64), (3, 16, 16, 16, 64, 64, (40.0, 4096, 32.0, 1.0), 16),
     (6, 32, 16, 32, 96, 160, (2.5, 1024, 24.0, 1.0), 32), (2, 8, 2, 8, 12, 12, (3.0, 8, 2.0, 1.0), 16),
-    (5, 12, 6, 20, 36, 20, (1.5, 40, 3.0, 1.0), 16)])
-def test_latent_attention_mixer_against_plain(dtype, heads, dn, dr, dv, rank, q_rank, scaling, page):
+    (5, 12, 6, 20, 36, 20, (1.5, 40, 3.0, 1.0), 16), (16, 32, 32, 32, 256, 96, (2.0, 32, 4.0, 0.5), 16),
+    (20, 16, 16, 24, 64, 48, None, 32), (33, 8, 16, 8, 192, 64, None, 16), (2, 16, 48, 16, 512, 32, None, 16)])
+@pytest.mark.parametrize("cores", [False, True])
+def test_latent_attention_mixer_against_plain(dtype, heads, dn, dr, dv, rank, q_rank, scaling, page, cores):
     """The mixer part alone: queries through a normed latent of their own, one normed latent row and one rotated key
-    part per token in the pages, neighbouring pairs with rescaled frequencies and magnitude, no gate."""
+    part per token in the pages, neighbouring pairs with rescaled frequencies and magnitude, no gate; steps of few
+    tokens on the tensor-core kernel (where the sizes fit it) and on the CUDA-core kernel."""
+    from llm_rs_b200 import ops
+    if cores and not ops.latent_decode_takes_mma(dtype, rank, dr, page):
+        pytest.skip("these sizes have one kernel for steps of few tokens")
     part, w, planes, m, g, D = _latent_setup(dtype, heads, dn, dr, dv, rank, q_rank, scaling, page, 128, rank + heads)
     seqs = [_rounded(torch.randn(n, D, generator=g), dtype) for n in (151, 42)]
     want = [P.latent_attention(s.double(), m, _double(w), "m.", 1e-5) for s in seqs]
-    got = _run_in_cuts(part, planes, seqs, CUTS, page, dtype, g, 128)
+    ops.latent_decode_mma(not cores)
+    try:
+        got = _run_in_cuts(part, planes, seqs, CUTS, page, dtype, g, 128)
+    finally:
+        ops.latent_decode_mma(True)
     for r in range(2):
         _close(got[r], want[r], dtype, r, bf16=0.04)     # a magnitude above 1 on both sides sharpens the softmax
 
