@@ -6,7 +6,8 @@ from .qwen3 import Qwen3Config
 from .rusadra import RusadraConfig
 from .pusazen import PusazenConfig
 from .pozelix import PozelixConfig
+from .fekolorn import FekolornConfig
 
 __all__ = ["ConfigError", "ArchitectureEntry", "architecture_names", "load_config",
            "register_architecture", "resolve_architecture", "unregister_architecture", "Qwen3Config", "RusadraConfig",
-           "PusazenConfig", "PozelixConfig"]
+           "PusazenConfig", "PozelixConfig", "FekolornConfig"]

@@ -5,8 +5,11 @@
 //   mask   causal (key <= query), plus one of
 //            window  key > query - size
 //            chunk   floor(key / size) == floor(query / size), chunks counted from position 0 of the sequence
+//   bias   with a table `bias` [bias_len, query heads] (float32): score += bias[min(query - key, bias_len - 1), head],
+//          after the scale and the cap (a learned bias per distance, laid out per distance by the caller)
 //   weights  exp(score - m) / (sum over visible keys + exp(sink_h - m)); the sink (one learned number per query head)
 //            has no key and no value: it only takes weight away. Null: no sink.
+//   output   the weighted sum of the values times `out_scale`
 //
 // A page holds, per key/value head, page_size rows of dk (keys) and then page_size rows of dv (values).
 //
@@ -32,7 +35,14 @@ struct ScoreOpts {
   float scale, softcap;
   const float* sink;
   int mask, size;
+  const float* bias;      // [bias_len, bias_heads] or null
+  int bias_len, bias_heads;
+  float out_scale;
 };
+// The bias of a key `dist` positions behind its query, for one query head.
+__device__ __forceinline__ float dist_bias(const ScoreOpts& o, int head, int dist) {
+  return o.bias[(size_t)min(max(dist, 0), o.bias_len - 1) * o.bias_heads + min(head, o.bias_heads - 1)];
+}
 
 __device__ __forceinline__ int first_visible(const ScoreOpts& o, int pos) {
   if (o.mask == MASK_WINDOW) return max(0, pos - o.size + 1);
@@ -89,7 +99,9 @@ __global__ void scored_prepare_kernel(T* __restrict__ q, long long q_stride, con
                                       const double* __restrict__ inv_freq, const int* __restrict__ positions,
                                       const int* __restrict__ token_req, const int* __restrict__ block_table,
                                       int table_stride, T* __restrict__ cache, int n_q_heads, int n_kv_heads, int dk,
-                                      int dv, int rot_dims, int page_size, float eps, int unit_heads) {
+                                      int dv, int rot_dims, int page_size, float eps, int unit_heads, int unit_values,
+                                      const T* __restrict__ v_first, long long v_first_stride,
+                                      const float* __restrict__ v_mix) {
   extern __shared__ float sm[];
   __shared__ float red[33];
   const int t = blockIdx.x, pos = positions[t];
@@ -129,6 +141,36 @@ __global__ void scored_prepare_kernel(T* __restrict__ q, long long q_stride, con
     }
     return a;
   };
+  // The values as the pages keep them: with `unit_values` every head's value divided by its own root mean square (no
+  // weight), then with `v_first` mixed with another layer's values of the same token, (1 - m) v + m v_first.
+  auto write_values = [&](int page, int slot) {
+    const float mix = v_first ? v_mix[0] : 0.f;
+    auto mixed = [&](float val, int c) {
+      return v_first ? (1.0f - mix) * val + mix * to_float(v_first[(size_t)t * v_first_stride + c]) : val;
+    };
+    auto place = [&](int head, int i) {
+      return page_head_offset(page, head, n_kv_heads, page_size, dk, dv) + (size_t)page_size * dk + (size_t)slot * dv + i;
+    };
+    if (unit_values) {
+      const int lane = threadIdx.x & 31;
+      for (int head = threadIdx.x >> 5; head < n_kv_heads; head += blockDim.x >> 5) {
+        const T* src = v + (size_t)t * v_stride + (size_t)head * dv;
+        float ss = 0.f;
+        for (int i = lane; i < dv; i += 32) {
+          const float f = to_float(src[i]);
+          ss = fmaf(f, f, ss);
+        }
+        const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
+        for (int i = lane; i < dv; i += 32)
+          cache[place(head, i)] = from_float<T>(mixed(to_float(src[i]) * inv, head * dv + i));
+      }
+    } else if (v_first) {
+      for (int c = threadIdx.x; c < n_kv_heads * dv; c += blockDim.x)
+        cache[place(c / dv, c % dv)] = from_float<T>(mixed(to_float(v[(size_t)t * v_stride + c]), c));
+    } else {
+      for (int c = threadIdx.x; c < n_kv_heads * dv; c += blockDim.x) cache[place(c / dv, c % dv)] = v[(size_t)t * v_stride + c];
+    }
+  };
   if (unit_heads) {
     // Every head of q and k, AFTER its rotation, is divided by its own root mean square (no weight): a warp per head.
     const int page = k == nullptr ? 0 :
@@ -149,11 +191,7 @@ __global__ void scored_prepare_kernel(T* __restrict__ q, long long q_stride, con
       for (int i = lane; i < dk; i += 32) dst[i] = from_float<T>(turned(x, nullptr, 1.0f, head, i) * inv);
     }
     if (k == nullptr) return;
-    for (int c = threadIdx.x; c < n_kv_heads * dv; c += blockDim.x) {
-      const int head = c / dv, i = c % dv;
-      cache[page_head_offset(page, head, n_kv_heads, page_size, dk, dv) + (size_t)page_size * dk + (size_t)slot * dv + i] =
-          v[(size_t)t * v_stride + c];
-    }
+    write_values(page, slot);
     return;
   }
   for (int c = threadIdx.x; c < wq; c += blockDim.x)
@@ -166,24 +204,24 @@ __global__ void scored_prepare_kernel(T* __restrict__ q, long long q_stride, con
     cache[page_head_offset(page, head, n_kv_heads, page_size, dk, dv) + (size_t)slot * dk + i] =
         from_float<T>(turned(xk, k_norm_w, inv_k, head, i));
   }
-  for (int c = threadIdx.x; c < n_kv_heads * dv; c += blockDim.x) {
-    const int head = c / dv, i = c % dv;
-    cache[page_head_offset(page, head, n_kv_heads, page_size, dk, dv) + (size_t)page_size * dk + (size_t)slot * dv + i] =
-        v[(size_t)t * v_stride + c];
-  }
+  write_values(page, slot);
 }
 
 // q: [tokens, n_q_heads * dk] rewritten in place; k, v: the new keys and values (null: the entry reads another
-// entry's pages and writes none); cache: one entry's pages.
+// entry's pages and writes none); cache: one entry's pages. unit_values: every head's value is divided by its root mean
+// square before it is kept; v_first ([tokens, n_kv_heads * dv], rows v_first_stride apart) with v_mix (one float on the
+// device): the kept value is (1 - v_mix) v + v_mix v_first.
 LLMRS_API int llmrs_scored_prepare(void* q, long long q_stride, const void* k, long long k_stride, const void* v,
                                    long long v_stride, int dtype, const float* q_norm_w, const float* k_norm_w,
                                    const double* inv_freq, const int* positions, const int* token_req,
                                    const int* block_table, int table_stride, void* cache, int n_tokens, int n_q_heads,
                                    int n_kv_heads, int dk, int dv, int rot_dims, int page_size, float eps,
-                                   int unit_heads, cudaStream_t stream) {
+                                   int unit_heads, int unit_values, const void* v_first, long long v_first_stride,
+                                   const float* v_mix, cudaStream_t stream) {
   LLMRS_REQUIRE(n_tokens >= 0 && n_q_heads > 0 && n_kv_heads > 0 && dk > 0 && dv > 0 && page_size > 0,
                 "scored_prepare: bad sizes");
   LLMRS_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dk, "scored_prepare: rot_dims %d of %d", rot_dims, dk);
+  LLMRS_REQUIRE(v_first == nullptr || v_mix != nullptr, "scored_prepare: values to mix in, but no weight");
   if (n_tokens == 0) return 0;
   const size_t smem = ((size_t)(n_q_heads + n_kv_heads) * dk + rot_dims) * sizeof(float);
   LLMRS_REQUIRE(smem <= 160 * 1024, "scored_prepare: rows of %zu bytes are too wide", smem);
@@ -200,7 +238,7 @@ LLMRS_API int llmrs_scored_prepare(void* q, long long q_stride, const void* k, l
     scored_prepare_kernel<T><<<n_tokens, threads, smem, stream>>>(                                                  \
         (T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, q_norm_w, k_norm_w, inv_freq, positions,     \
         token_req, block_table, table_stride, (T*)cache, n_q_heads, n_kv_heads, dk, dv, rot_dims, page_size, eps,   \
-        unit_heads);                                                                                                \
+        unit_heads, unit_values, (const T*)v_first, v_first_stride, v_mix);                                         \
   } while (0)
   if (dtype == LLMRS_F32) LLMRS_SP_LAUNCH(float);
   else if (dtype == LLMRS_BF16) LLMRS_SP_LAUNCH(__nv_bfloat16);
@@ -311,7 +349,7 @@ scored_prefill_kernel(const T* __restrict__ q, long long q_stride, T* __restrict
       float dot = 0.f;
       for (int e = 0; e < dk; ++e) dot = fmaf(qr[e], kr[e], dot);
       const bool seen = r < rows && key <= my_pos && key >= my_lo;
-      s[jj] = seen ? capped(opt, dot) : -INFINITY;
+      s[jj] = seen ? capped(opt, dot) + (opt.bias ? dist_bias(opt, head, my_pos - key) : 0.f) : -INFINITY;
     }
     float bm = s[0];
 #pragma unroll
@@ -355,7 +393,7 @@ scored_prefill_kernel(const T* __restrict__ q, long long q_stride, T* __restrict
       w = expf(m - mf);
       l = l * w + expf(sk - mf);
     }
-    const float inv = l > 0.f ? w / l : 0.f;
+    const float inv = l > 0.f ? w / l * opt.out_scale : 0.f;
     T* o = out + (size_t)(tok0 + r) * out_stride + (size_t)head * dv;
 #pragma unroll
     for (int j = 0; j < SP_MAX_VCH; ++j)
@@ -477,7 +515,17 @@ scored_prefill_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* 
       // Only a tile that touches the diagonal, or in which some row's first visible key lies, has scores to hide.
       const int pw = pos0 + warp * 16;
       const bool need_mask = kb + SM_BK - 1 > pw || kb < last_lo;
-      if (need_mask) {
+      if (opt.bias) {
+#pragma unroll
+        for (int n = 0; n < SM_BK / 8; ++n)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = kb + n * 8 + tq * 2 + (e & 1);
+            const bool seen = key <= pos_r[e >> 1] && key >= lo_r[e >> 1];
+            s[n][e] = seen ? fmaf(dist_bias(opt, head, pos_r[e >> 1] - key), LOG2E, cap(s[n][e])) : -INFINITY;
+            mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+          }
+      } else if (need_mask) {
 #pragma unroll
         for (int n = 0; n < SM_BK / 8; ++n)
 #pragma unroll
@@ -552,7 +600,7 @@ scored_prefill_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* 
         w = ex2_fast(m_row[r] - mf);
         l = l * w + ex2_fast(sk - mf);
       }
-      const float inv = l > 0.f ? w / l : 0.f;
+      const float inv = l > 0.f ? w / l * opt.out_scale : 0.f;
       bf16* orow = out + (size_t)(tok0 + row) * out_stride + (size_t)head * DV;
 #pragma unroll
       for (int n = 0; n < 2 * VCH; ++n)
@@ -598,14 +646,15 @@ LLMRS_API void llmrs_scored_generic_only(int on) { g_scored_generic_only = on; }
 // Head sizes the tensor-core kernel is built for (keys, values), in units of 16.
 #define LLMRS_SCORED_MMA_SIZES(X)                                                                              \
   X(1, 1) X(2, 2) X(3, 3) X(4, 4) X(5, 5) X(6, 6) X(7, 7) X(8, 8) X(1, 2) X(2, 1) X(2, 3) X(3, 2) X(2, 4) X(4, 2) \
-  X(3, 4) X(4, 3) X(4, 6) X(6, 4) X(4, 8) X(8, 4) X(6, 8) X(8, 6) X(12, 8)
+  X(3, 4) X(4, 3) X(4, 6) X(6, 4) X(4, 8) X(8, 4) X(6, 8) X(8, 6) X(12, 8) X(6, 2) X(8, 2)
 
 LLMRS_API int llmrs_scored_prefill(const void* q, long long q_stride, void* out, long long out_stride,
                                    const void* cache, const int* tiles, int n_tiles, const int* q_start,
                                    const int* n_new, const int* cached_len, const int* block_table, int table_stride,
                                    int n_q_heads, int n_kv_heads, int dk, int dv, int page_size, float scale,
-                                   float softcap, const float* sink, int mask, int mask_size, int dtype,
-                                   int n_tokens, int n_pages, int prefer_tc, cudaStream_t stream) {
+                                   float softcap, const float* sink, int mask, int mask_size, const float* bias,
+                                   int bias_len, float out_scale, int dtype, int n_tokens, int n_pages, int prefer_tc,
+                                   cudaStream_t stream) {
   LLMRS_REQUIRE(n_tiles >= 0 && n_q_heads > 0 && n_kv_heads > 0 && page_size > 0, "scored_prefill: bad sizes");
   LLMRS_REQUIRE(n_q_heads % n_kv_heads == 0, "scored_prefill: %d query heads are no multiple of %d key heads",
                 n_q_heads, n_kv_heads);
@@ -613,13 +662,15 @@ LLMRS_API int llmrs_scored_prefill(const void* q, long long q_stride, void* out,
                 dk, dv);
   LLMRS_REQUIRE(mask == MASK_CAUSAL || ((mask == MASK_WINDOW || mask == MASK_CHUNK) && mask_size > 0),
                 "scored_prefill: mask %d with size %d", mask, mask_size);
+  LLMRS_REQUIRE(bias == nullptr || bias_len > 0, "scored_prefill: a bias table of %d rows", bias_len);
   if (n_tiles == 0) return 0;
-  ScoreOpts opt{scale, softcap, sink, mask, mask_size};
+  ScoreOpts opt{scale, softcap, sink, mask, mask_size, bias, bias_len, n_q_heads, out_scale};
   if ((long long)n_tiles * n_q_heads > 2147483647LL) return llmrs_fail("scored_prefill: %d tiles are too many", n_tiles);
   // Long portions of heads of 128 channels: the tcgen05 kernel (128-query blocks, K and V by TMA, scores in tensor
   // memory), with the cap, the sink and the mask in its softmax threads. Its waits are bounded; a block that gives
   // up leaves a code that llmrs_attention_tc_error reads.
   if (dtype == LLMRS_BF16 && prefer_tc && !g_scored_generic_only && dk == 128 && dv == 128 && n_tiles <= 8192 &&
+      bias == nullptr && out_scale == 1.0f &&
       out_stride % 8 == 0 && ((uintptr_t)out & 15) == 0 &&
       llmrs_attn_prefill_tc_supported(q, q_stride, cache, dk, page_size, scale))
     return llmrs_attn_prefill_tc_scored(q, q_stride, n_tokens, out, out_stride, cache,
@@ -743,7 +794,8 @@ scored_decode_kernel(const T* __restrict__ q, long long q_stride, const T* __res
       float dot = 0.f;
 #pragma unroll
       for (int j = 0; j < SD_MAXC; ++j) dot = fmaf(qr[j], kf[u][j], dot);
-      sc[u] = key0 + u < k_end ? capped(opt, warp_sum(dot)) : -INFINITY;      // the first of the four always counts
+      sc[u] = key0 + u < k_end ? capped(opt, warp_sum(dot)) + (opt.bias ? dist_bias(opt, head, pos - key0 - u) : 0.f)
+                               : -INFINITY;      // the first of the four always counts
       m_new = fmaxf(m_new, sc[u]);
     }
     const float corr = expf(m - m_new);
@@ -900,7 +952,8 @@ scored_decode_grouped_kernel(const T* __restrict__ q, long long q_stride, const 
     float p[GH];
 #pragma unroll
     for (int h = 0; h < GH; ++h) {
-      const float s = seen ? capped(opt, dot[h]) : -INFINITY;      // lane 0's key always counts
+      const float s = seen ? capped(opt, dot[h]) + (opt.bias ? dist_bias(opt, head0 + h, pos - key) : 0.f)
+                           : -INFINITY;      // lane 0's key always counts
       const float m_new = fmaxf(m[h], warp_max(s));
       const float corr = expf(m[h] - m_new);
       p[h] = seen ? expf(s - m_new) : 0.f;
@@ -973,7 +1026,8 @@ scored_decode_grouped_kernel(const T* __restrict__ q, long long q_stride, const 
 template <typename T>
 __global__ void scored_decode_merge_kernel(const float* __restrict__ part, T* __restrict__ out, long long out_stride,
                                            const int* __restrict__ dec_reqs, const int* __restrict__ q_start,
-                                           int max_splits, int n_q_heads, int dv, const float* __restrict__ sink) {
+                                           int max_splits, int n_q_heads, int dv, const float* __restrict__ sink,
+                                           float out_scale) {
   const int di = blockIdx.x, head = blockIdx.y;
   const float* base = part + ((size_t)di * n_q_heads + head) * max_splits * sd_part_stride(dv);
   float m = sink ? sink[head] : -INFINITY;
@@ -983,7 +1037,7 @@ __global__ void scored_decode_merge_kernel(const float* __restrict__ part, T* __
     const float* pp = base + (size_t)s * sd_part_stride(dv);
     if (pp[0] > -INFINITY) l += pp[1] * expf(pp[0] - m);
   }
-  const float inv = l > 0.f ? 1.0f / l : 0.f;
+  const float inv = l > 0.f ? out_scale / l : 0.f;
   T* o = out + (size_t)q_start[dec_reqs[di]] * out_stride + (size_t)head * dv;
   for (int c = threadIdx.x; c < dv; c += blockDim.x) {
     float a = 0.f;
@@ -1018,7 +1072,8 @@ LLMRS_API int llmrs_scored_decode(const void* q, long long q_stride, void* out, 
                                   const int* cached_len, const int* block_table, int table_stride, float* scratch,
                                   int max_splits, int split_keys, int n_q_heads, int n_kv_heads, int dk, int dv,
                                   int page_size, float scale, float softcap, const float* sink, int mask,
-                                  int mask_size, int dtype, cudaStream_t stream) {
+                                  int mask_size, const float* bias, int bias_len, float out_scale, int dtype,
+                                  cudaStream_t stream) {
   LLMRS_REQUIRE(n_dec >= 0 && n_q_heads > 0 && n_kv_heads > 0 && page_size > 0 && max_splits > 0 && split_keys > 0,
                 "scored_decode: bad sizes");
   LLMRS_REQUIRE(n_q_heads % n_kv_heads == 0, "scored_decode: %d query heads are no multiple of %d key heads",
@@ -1027,8 +1082,9 @@ LLMRS_API int llmrs_scored_decode(const void* q, long long q_stride, void* out, 
   LLMRS_REQUIRE(mask == MASK_CAUSAL || ((mask == MASK_WINDOW || mask == MASK_CHUNK) && mask_size > 0),
                 "scored_decode: mask %d with size %d", mask, mask_size);
   LLMRS_REQUIRE(n_q_heads <= 65535 && max_splits <= 65535, "scored_decode: too many heads or runs");
+  LLMRS_REQUIRE(bias == nullptr || bias_len > 0, "scored_decode: a bias table of %d rows", bias_len);
   if (n_dec == 0) return 0;
-  ScoreOpts opt{scale, softcap, sink, mask, mask_size};
+  ScoreOpts opt{scale, softcap, sink, mask, mask_size, bias, bias_len, n_q_heads, out_scale};
   dim3 grid(n_dec, n_q_heads, max_splits), mgrid(n_dec, n_q_heads);
   const size_t smem = (size_t)SD_WARPS * dv * sizeof(float);
   // Rows of a multiple of four channels that start on a load's boundary are read four channels a load.
@@ -1071,13 +1127,13 @@ LLMRS_API int llmrs_scored_decode(const void* q, long long q_stride, void* out, 
     int rc = llmrs_launch_status("scored_decode");
     if (rc) return rc;
     scored_decode_merge_kernel<float><<<mgrid, 64, 0, stream>>>(scratch, (float*)out, out_stride, dec_reqs, q_start,
-                                                                max_splits, n_q_heads, dv, sink);
+                                                                max_splits, n_q_heads, dv, sink, out_scale);
   } else if (dtype == LLMRS_BF16) {
     LLMRS_SD_LAUNCH(bf16);
     int rc = llmrs_launch_status("scored_decode");
     if (rc) return rc;
     scored_decode_merge_kernel<bf16><<<mgrid, 64, 0, stream>>>(scratch, (bf16*)out, out_stride, dec_reqs, q_start,
-                                                               max_splits, n_q_heads, dv, sink);
+                                                               max_splits, n_q_heads, dv, sink, out_scale);
   } else {
     return llmrs_fail("scored_decode: unknown dtype %d", dtype);
   }

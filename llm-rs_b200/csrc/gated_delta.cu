@@ -1,0 +1,274 @@
+// Gated delta rule: a recurrent mixer with a matrix state S [key channel, value channel] per head,
+//
+//   S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q          (the read-out sees the token's own write)
+//
+// g in (0, 1) and beta in (0, 1) are one number per head and token. q and k (G heads of d channels; value head h reads
+// q/k head h / (H / G)) and v (H heads of dv channels) each pass a short causal convolution over time per channel
+// (K taps, the last one the current token's, zeros before a sequence's start) and SiLU; q and k are then made unit
+// vectors per head (x / sqrt(sum x^2 + key_eps)), q is also multiplied by q_scale. g = exp(-exp(A_log_h) *
+// softplus(a + dt_bias_h)) and beta = sigmoid(b) come from two float32 projections a, b. After the recurrence each head's
+// o is divided by its root mean square over dv, multiplied by a weight of size dv (shared by the heads) and by
+// SiLU(gate). Everything but the projections' inputs is float32.
+//
+// Per-request state: S (float32 [slots, H, d, dv]) and the last K - 1 rows that entered the convolutions
+// (float32 [slots, K - 1, C], C = 2 G d + H dv: the q, k and v channels side by side, oldest row first).
+//
+//   prepare      a block per token: convolutions + SiLU, unit q and k, g and beta, as float32 rows
+//   conv state   a block per request, after prepare: the request's last K - 1 convolution inputs
+//   recurrence   a block per (request, head, slice of 16 value columns) walks the request's tokens in order; four
+//                neighbouring lanes share a column, each with a quarter of the key channels in registers; k^T S and
+//                q^T S are summed over the four by two shuffles. Rows come in chunks through two shared-memory buffers.
+//   output       a warp per (token, head): norm, weight, gate
+#include "common.cuh"
+#include "mma_util.cuh"
+
+__device__ __forceinline__ float gd_silu(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float gd_softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+
+template <typename TA>
+__global__ void gdr_prepare_kernel(const TA* __restrict__ x, long long stride, const float* __restrict__ taps,
+                                   const float* __restrict__ ba, const float* __restrict__ a_log,
+                                   const float* __restrict__ dt_bias, const float* __restrict__ conv_state,
+                                   const int* __restrict__ token_req, const int* __restrict__ q_start,
+                                   const int* __restrict__ slot_ids, float* __restrict__ pq, float* __restrict__ pk,
+                                   float* __restrict__ pv, float* __restrict__ pbeta, float* __restrict__ pg, int G,
+                                   int H, int d, int dv, int K, float key_eps, float q_scale) {
+  extern __shared__ float row[];      // [C] after convolution and SiLU
+  const int t = blockIdx.x, req = token_req[t], off = t - q_start[req];
+  const int wq = G * d, wv = H * dv, C = 2 * wq + wv;
+  const float* tail = conv_state + (size_t)slot_ids[req] * (K - 1) * C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < K; ++j) {      // lag j: the input of j tokens ago
+      const int o = off - j;
+      const float in = o >= 0 ? to_float(x[(size_t)(t - j) * stride + c]) : tail[(size_t)(K - 1 + o) * C + c];
+      acc = fmaf(taps[(size_t)c * K + (K - 1 - j)], in, acc);
+    }
+    row[c] = gd_silu(acc);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int hh = warp; hh < 2 * G; hh += nwarps) {      // q heads, then k heads
+    const float* src = row + (size_t)hh * d;
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) ss = fmaf(src[i], src[i], ss);
+    const float inv = 1.0f / sqrtf(warp_sum(ss) + key_eps) * (hh < G ? q_scale : 1.0f);
+    float* dst = hh < G ? pq + (size_t)t * wq + (size_t)hh * d : pk + (size_t)t * wq + (size_t)(hh - G) * d;
+    for (int i = lane; i < d; i += 32) dst[i] = src[i] * inv;
+  }
+  for (int c = threadIdx.x; c < wv; c += blockDim.x) pv[(size_t)t * wv + c] = row[2 * wq + c];
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    pbeta[(size_t)t * H + h] = 1.0f / (1.0f + expf(-ba[(size_t)t * 2 * H + h]));
+    pg[(size_t)t * H + h] = expf(-expf(a_log[h]) * gd_softplus(ba[(size_t)t * 2 * H + H + h] + dt_bias[h]));
+  }
+}
+
+template <typename TA>
+__global__ void gdr_conv_state_kernel(const TA* __restrict__ x, long long stride, float* __restrict__ conv_state,
+                                      const int* __restrict__ q_start, const int* __restrict__ n_new,
+                                      const int* __restrict__ slot_ids, int C, int K) {
+  const int req = blockIdx.x, n = n_new[req], t0 = q_start[req];
+  float* tail = conv_state + (size_t)slot_ids[req] * (K - 1) * C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x)
+    for (int j = 0; j < K - 1; ++j) {      // ascending: an old row is read before the place it moves from is overwritten
+      const int o = n - (K - 1) + j;
+      tail[(size_t)j * C + c] = o >= 0 ? to_float(x[(size_t)(t0 + o) * stride + c]) : tail[(size_t)(j + n) * C + c];
+    }
+}
+
+constexpr int GD_COLS = 16, GD_LANES = 4, GD_THREADS = GD_COLS * GD_LANES;
+
+template <int DMAX>
+__global__ void __launch_bounds__(GD_THREADS)
+gdr_recurrence_kernel(const float* __restrict__ pq, const float* __restrict__ pk, const float* __restrict__ pv,
+                      const float* __restrict__ pbeta, const float* __restrict__ pg, float* __restrict__ state,
+                      const int* __restrict__ q_start, const int* __restrict__ n_new,
+                      const int* __restrict__ slot_ids, float* __restrict__ o_raw, int G, int H, int d, int dv) {
+  constexpr int CHUNK = DMAX >= 256 ? 8 : 16;
+  constexpr int IPL = DMAX / GD_LANES;             // key channels per lane
+  __shared__ __align__(16) float s_qk[2][2][CHUNK][DMAX];      // q, k of a chunk's tokens; channels >= d stay 0
+  __shared__ float s_v[2][CHUNK][GD_COLS], s_bg[2][2][CHUNK];
+  const int req = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * GD_COLS;
+  const int kh = head / (H / G);
+  const int tid = threadIdx.x;
+  const int col = col0 + tid / GD_LANES, part = tid % GD_LANES, i0 = part * IPL;
+  const bool live = col < dv;
+  const int t0 = q_start[req], n = n_new[req];
+  const int wq = G * d, wv = H * dv;
+  float* S_g = state + ((size_t)slot_ids[req] * H + head) * d * dv;
+  float S[IPL];
+#pragma unroll
+  for (int i = 0; i < IPL; ++i) S[i] = (live && i0 + i < d) ? S_g[(size_t)(i0 + i) * dv + col] : 0.f;
+  for (int e = tid; e < 2 * 2 * CHUNK * DMAX; e += GD_THREADS) (&s_qk[0][0][0][0])[e] = 0.f;
+  for (int e = tid; e < 2 * CHUNK * GD_COLS; e += GD_THREADS) (&s_v[0][0][0])[e] = 0.f;
+  __syncthreads();
+  const bool wide = d % 4 == 0;      // every row then starts on a 16-byte boundary
+  const int ncols = min(GD_COLS, dv - col0);
+  auto load_chunk = [&](int buf, int c0) {
+    const int cn = min(CHUNK, n - c0);
+    if (wide) {
+      const int per_row = d / 4;
+      for (int e = tid; e < 2 * cn * per_row; e += GD_THREADS) {
+        const int a = e / (cn * per_row), rem = e % (cn * per_row), tt = rem / per_row, piece = rem % per_row;
+        const float* src = (a == 0 ? pq : pk) + (size_t)(t0 + c0 + tt) * wq + (size_t)kh * d + piece * 4;
+        cp_async_16(&s_qk[buf][a][tt][piece * 4], src, 16);
+      }
+    } else {
+      for (int e = tid; e < 2 * cn * d; e += GD_THREADS) {
+        const int a = e / (cn * d), rem = e % (cn * d), tt = rem / d, i = rem % d;
+        s_qk[buf][a][tt][i] = (a == 0 ? pq : pk)[(size_t)(t0 + c0 + tt) * wq + (size_t)kh * d + i];
+      }
+    }
+    for (int e = tid; e < cn * ncols; e += GD_THREADS) {
+      const int tt = e / ncols, c = e % ncols;
+      s_v[buf][tt][c] = pv[(size_t)(t0 + c0 + tt) * wv + (size_t)head * dv + col0 + c];
+    }
+    for (int e = tid; e < 2 * cn; e += GD_THREADS) {
+      const int a = e / cn, tt = e % cn;
+      s_bg[buf][a][tt] = (a == 0 ? pbeta : pg)[(size_t)(t0 + c0 + tt) * H + head];
+    }
+    cp_async_commit();
+  };
+
+  if (n > 0) load_chunk(0, 0);
+  for (int c0 = 0, it = 0; c0 < n; c0 += CHUNK, ++it) {
+    const int cn = min(CHUNK, n - c0), buf = it & 1;
+    if (c0 + CHUNK < n) {
+      load_chunk(buf ^ 1, c0 + CHUNK);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int tt = 0; tt < cn; ++tt) {
+      const float vj = s_v[buf][tt][tid / GD_LANES], beta = s_bg[buf][0][tt], g = s_bg[buf][1][tt];
+      float ks[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < IPL; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(&s_qk[buf][1][tt][i0 + i]);
+        S[i] *= g; S[i + 1] *= g; S[i + 2] *= g; S[i + 3] *= g;
+        ks[0] = fmaf(k4.x, S[i], ks[0]);
+        ks[1] = fmaf(k4.y, S[i + 1], ks[1]);
+        ks[2] = fmaf(k4.z, S[i + 2], ks[2]);
+        ks[3] = fmaf(k4.w, S[i + 3], ks[3]);
+      }
+      float kS = (ks[0] + ks[1]) + (ks[2] + ks[3]);
+      kS += __shfl_xor_sync(0xffffffffu, kS, 1);
+      kS += __shfl_xor_sync(0xffffffffu, kS, 2);
+      const float u = beta * (vj - kS);
+      float os[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < IPL; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(&s_qk[buf][1][tt][i0 + i]);
+        const float4 q4 = *reinterpret_cast<const float4*>(&s_qk[buf][0][tt][i0 + i]);
+        S[i] = fmaf(k4.x, u, S[i]);
+        S[i + 1] = fmaf(k4.y, u, S[i + 1]);
+        S[i + 2] = fmaf(k4.z, u, S[i + 2]);
+        S[i + 3] = fmaf(k4.w, u, S[i + 3]);
+        os[0] = fmaf(S[i], q4.x, os[0]);
+        os[1] = fmaf(S[i + 1], q4.y, os[1]);
+        os[2] = fmaf(S[i + 2], q4.z, os[2]);
+        os[3] = fmaf(S[i + 3], q4.w, os[3]);
+      }
+      float o = (os[0] + os[1]) + (os[2] + os[3]);
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (part == 0 && live) o_raw[(size_t)(t0 + c0 + tt) * wv + (size_t)head * dv + col] = o;
+    }
+    __syncthreads();
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < IPL; ++i)
+      if (i0 + i < d) S_g[(size_t)(i0 + i) * dv + col] = S[i];
+  }
+}
+
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight[:] * silu(gate[t, h, :]); a warp per (t, h).
+template <typename TA>
+__global__ void gdr_out_kernel(const float* __restrict__ o_raw, const TA* __restrict__ gate, long long gate_stride,
+                               const float* __restrict__ norm_w, TA* __restrict__ out, long long out_stride,
+                               int n_rows, int H, int dv, float eps, float out_scale) {
+  const int r = blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= n_rows) return;
+  const int t = r / H, h = r % H;
+  const float* o = o_raw + (size_t)t * H * dv + (size_t)h * dv;
+  float ss = 0.f;
+  for (int i = lane; i < dv; i += 32) ss = fmaf(o[i], o[i], ss);
+  const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps) * out_scale;
+  for (int i = lane; i < dv; i += 32) {
+    const float gt = gd_silu(to_float(gate[(size_t)t * gate_stride + (size_t)h * dv + i]));
+    out[(size_t)t * out_stride + (size_t)h * dv + i] = from_float<TA>(o[i] * inv * norm_w[i] * gt);
+  }
+}
+
+// Float32 workspace of the kernels, in floats: prepared q, k, v, beta, g and the raw read-outs.
+LLMRS_API long long llmrs_gated_delta_work_floats(int n_tokens, int G, int H, int d, int dv) {
+  return (long long)n_tokens * (2LL * G * d + 2LL * H * dv + 2LL * H) + 16;
+}
+
+// x: [tokens, >= 2 G d + H dv] of `dtype`, rows `x_stride` apart: the q, k and v channels that enter the convolutions;
+// gate: [tokens, H dv] rows `gate_stride` apart; taps: float32 [2 G d + H dv, K]; ba: float32 [tokens, 2 H] (b, then
+// a); state: float32 [slots, H, d, dv]; conv_state: float32 [slots, K - 1, 2 G d + H dv]; work: 16-byte aligned;
+// out: [tokens, H dv] rows `out_stride` apart, multiplied by `out_scale`.
+LLMRS_API int llmrs_gated_delta(const void* x, long long x_stride, const void* gate, long long gate_stride, int dtype,
+                                const float* taps, const float* ba, const float* a_log, const float* dt_bias,
+                                const float* norm_w, float* state, float* conv_state, const int* token_req,
+                                const int* q_start, const int* n_new, const int* slot_ids, float* work, void* out,
+                                long long out_stride, int n_tokens, int n_requests, int G, int H, int d, int dv, int K,
+                                float key_eps, float q_scale, float norm_eps, float out_scale, cudaStream_t stream) {
+  LLMRS_REQUIRE(n_requests >= 0 && n_tokens >= 0 && G > 0 && H > 0 && d > 0 && dv > 0 && K >= 1, "gated_delta: bad sizes");
+  LLMRS_REQUIRE(H % G == 0, "gated_delta: %d value heads are no multiple of %d key heads", H, G);
+  LLMRS_REQUIRE(d <= 256, "gated_delta: key heads of at most 256 channels, got %d", d);
+  LLMRS_REQUIRE(H <= 65535 && (dv + GD_COLS - 1) / GD_COLS <= 65535, "gated_delta: too many heads or columns");
+  LLMRS_REQUIRE(((uintptr_t)work & 15) == 0, "gated_delta: the workspace must be 16-byte aligned");
+  if (n_requests == 0 || n_tokens == 0) return 0;
+  const int wq = G * d, wv = H * dv, C = 2 * wq + wv;
+  LLMRS_REQUIRE((size_t)C * sizeof(float) <= 160 * 1024, "gated_delta: %d convolution channels are too many", C);
+  // Every piece starts on a 16-byte boundary (the recurrence copies q and k rows sixteen bytes at a time).
+  auto up4 = [](size_t v) { return (v + 3) & ~(size_t)3; };
+  float* pq = work;
+  float* pk = pq + up4((size_t)n_tokens * wq);
+  float* pv = pk + up4((size_t)n_tokens * wq);
+  float* pbeta = pv + up4((size_t)n_tokens * wv);
+  float* pg = pbeta + (size_t)n_tokens * H;
+  float* o_raw = pg + (size_t)n_tokens * H;
+  const size_t smem = (size_t)C * sizeof(float);
+  const int dmax = d <= 32 ? 32 : (d <= 64 ? 64 : (d <= 128 ? 128 : 256));
+  dim3 grid(n_requests, H, (dv + GD_COLS - 1) / GD_COLS);
+  const int rows = n_tokens * H;
+#define LLMRS_GD_LAUNCH(T)                                                                                             \
+  do {                                                                                                                 \
+    static size_t configured = 48 * 1024;                                                                              \
+    if (smem > configured) {                                                                                           \
+      cudaError_t e = cudaFuncSetAttribute(gdr_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return llmrs_fail("gated_delta: shared memory %zu: %s", smem, cudaGetErrorString(e));      \
+      configured = smem;                                                                                               \
+    }                                                                                                                  \
+    gdr_prepare_kernel<T><<<n_tokens, 256, smem, stream>>>((const T*)x, x_stride, taps, ba, a_log, dt_bias, conv_state, \
+                                                           token_req, q_start, slot_ids, pq, pk, pv, pbeta, pg, G, H,  \
+                                                           d, dv, K, key_eps, q_scale);                                \
+    int rc = llmrs_launch_status("gated_delta (prepare)");                                                             \
+    if (rc != 0) return rc;                                                                                            \
+    if (K > 1) {                                                                                                       \
+      gdr_conv_state_kernel<T><<<n_requests, 256, 0, stream>>>((const T*)x, x_stride, conv_state, q_start, n_new,      \
+                                                               slot_ids, C, K);                                        \
+      rc = llmrs_launch_status("gated_delta (convolution state)");                                                     \
+      if (rc != 0) return rc;                                                                                          \
+    }                                                                                                                  \
+    if (dmax == 32) gdr_recurrence_kernel<32><<<grid, GD_THREADS, 0, stream>>>(pq, pk, pv, pbeta, pg, state, q_start, n_new, slot_ids, o_raw, G, H, d, dv); \
+    else if (dmax == 64) gdr_recurrence_kernel<64><<<grid, GD_THREADS, 0, stream>>>(pq, pk, pv, pbeta, pg, state, q_start, n_new, slot_ids, o_raw, G, H, d, dv); \
+    else if (dmax == 128) gdr_recurrence_kernel<128><<<grid, GD_THREADS, 0, stream>>>(pq, pk, pv, pbeta, pg, state, q_start, n_new, slot_ids, o_raw, G, H, d, dv); \
+    else gdr_recurrence_kernel<256><<<grid, GD_THREADS, 0, stream>>>(pq, pk, pv, pbeta, pg, state, q_start, n_new, slot_ids, o_raw, G, H, d, dv); \
+    rc = llmrs_launch_status("gated_delta (recurrence)");                                                              \
+    if (rc != 0) return rc;                                                                                            \
+    gdr_out_kernel<T><<<(rows + 3) / 4, 128, 0, stream>>>(o_raw, (const T*)gate, gate_stride, norm_w, (T*)out,         \
+                                                          out_stride, rows, H, dv, norm_eps, out_scale);               \
+  } while (0)
+  if (dtype == LLMRS_F32) LLMRS_GD_LAUNCH(float);
+  else if (dtype == LLMRS_BF16) LLMRS_GD_LAUNCH(__nv_bfloat16);
+  else return llmrs_fail("gated_delta: unknown dtype %d", dtype);
+#undef LLMRS_GD_LAUNCH
+  return llmrs_launch_status("gated_delta (norm and gate)");
+}

@@ -68,6 +68,9 @@ class StepContext:
         self.want_rows = None
         self.block_tables: List[Optional[torch.Tensor]] = []
         self.plans: Dict[Hashable, PlanView] = {}
+        # Tensors that one part leaves for parts that run later in the same step (a layer's values that later layers
+        # mix into theirs), by a key the parts agree on. They live as long as the context.
+        self.shared: Dict[Hashable, torch.Tensor] = {}
         # (stream, its rows rounded to the activation type): left by a block whose last norm made the copy anyway,
         # for the block after it.
         self.stream_copy = None
@@ -134,9 +137,16 @@ class ModelRunner:
         self._planners: "OrderedDict[Hashable, object]" = OrderedDict()
         for step in spec.run_order:
             mixer = getattr(self.model.blocks[step.layer], "mixer", None)
-            key = mixer.plan_key() if mixer is not None and hasattr(mixer, "plan_key") else None
-            if key is not None and key not in self._planners:
-                self._planners[key] = mixer
+            if mixer is None:
+                continue
+            if hasattr(mixer, "planners"):       # a mixer made of several: each side that plans, under its own key
+                pairs = mixer.planners()
+            else:
+                key = mixer.plan_key() if hasattr(mixer, "plan_key") else None
+                pairs = [(key, mixer)] if key is not None else []
+            for key, planner in pairs:
+                if key not in self._planners:
+                    self._planners[key] = planner
         # Captured steps by (batch size, wanted rows, table widths, plans' shapes), least recently used first; a
         # captured step keeps its own logits and workspace, so their number is bounded.
         self._graphs: "OrderedDict[tuple, _DecodeGraph]" = OrderedDict()

@@ -1,5 +1,5 @@
 """Architectures: each module turns its typed configuration into a ``ModelSpec`` and
 registers itself by the name found in config.json."""
-from . import pozelix, pusazen, qwen3, rusadra
+from . import fekolorn, pozelix, pusazen, qwen3, rusadra
 
-__all__ = ["pozelix", "pusazen", "qwen3", "rusadra"]
+__all__ = ["fekolorn", "pozelix", "pusazen", "qwen3", "rusadra"]

@@ -1114,22 +1114,31 @@ MASK_CAUSAL, MASK_WINDOW, MASK_CHUNK = 0, 1, 2
 def scored_prepare(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], q_norm_w, k_norm_w,
                    inv_freq: torch.Tensor, ctx, table, cache: Optional[torch.Tensor], n_q_heads: int,
                    n_kv_heads: int, dk: int, dv: int, rot_dims: int, page_size: int, eps: float,
-                   unit_heads: bool = False) -> None:
+                   unit_heads: bool = False, unit_values: bool = False, v_first: Optional[torch.Tensor] = None,
+                   v_mix: Optional[torch.Tensor] = None) -> None:
     """Norm over the whole q and k rows, rotation, q rewritten in place, k and v into the pages ``cache``
     ([pages, kv heads, page_size * (dk + dv)]); with ``unit_heads`` every head of q and k is instead divided by its
-    own root mean square after the rotation (no weights); see ``csrc/attention_scored.cu``."""
+    own root mean square after the rotation (no weights); with ``unit_values`` every head of v by its own before it is
+    kept; with ``v_first`` (another layer's values of the same tokens) and ``v_mix`` (one float32 on the device) the
+    kept value is ``(1 - v_mix) v + v_mix v_first``; see ``csrc/attention_scored.cu``."""
     _need(q, "q", contiguous=False)
     _need(inv_freq, "inv_freq", torch.float64)
     if k is not None:
         _need(k, "k", q.dtype, contiguous=False)
         _need(v, "v", q.dtype, contiguous=False)
         _need(cache, "cache", q.dtype)
+    if v_first is not None:
+        _need(v_first, "v_first", q.dtype, contiguous=False)
+        _need(v_mix, "v_mix", torch.float32)
+        if v is None or v_first.shape != v.shape:
+            raise KernelError("scored_prepare: v_first must have the shape of v")
     _check(_lib().llmrs_scored_prepare(
         _ptr(q), _LL(_row_stride(q, "q")), _ptr(k), _LL(0 if k is None else _row_stride(k, "k")), _ptr(v),
         _LL(0 if v is None else _row_stride(v, "v")), dtype_code(q.dtype), _ptr(q_norm_w), _ptr(k_norm_w),
         _ptr(inv_freq), _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(table), 0 if table is None else table.size(1),
         _ptr(cache), q.size(0), n_q_heads, n_kv_heads, dk, dv, rot_dims, page_size, ctypes.c_float(eps),
-        int(bool(unit_heads)), _stream()), "scored_prepare")
+        int(bool(unit_heads)), int(bool(unit_values)), _ptr(v_first),
+        _LL(0 if v_first is None else _row_stride(v_first, "v_first")), _ptr(v_mix), _stream()), "scored_prepare")
 
 
 def scored_generic_only(on: bool) -> None:
@@ -1141,18 +1150,29 @@ def scored_generic_only(on: bool) -> None:
 
 def scored_prefill(q, out, cache, tiles, n_tiles: int, ctx, table, n_q_heads: int, n_kv_heads: int, dk: int, dv: int,
                    page_size: int, scale: float, softcap: float, sink, mask: int, mask_size: int,
-                   prefer_tc: bool = False) -> None:
+                   prefer_tc: bool = False, bias: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> None:
     """Prompt portions (tiles of 64 queries: request, offset) through ``csrc/attention_scored.cu``. ``prefer_tc`` asks
     for the tcgen05 kernel where it applies (bfloat16, keys and values of 128 channels, pages of a multiple of 16
-    keys; worth it when the portions are long)."""
+    keys; worth it when the portions are long). ``bias``: float32 [distances, query heads], added to the score of a
+    key that many positions behind its query (the last row for every greater distance); ``out_scale`` multiplies
+    the output."""
     _need(q, "q", contiguous=False)
     _need(out, "out", q.dtype, contiguous=False)
     _need(cache, "cache", q.dtype)
+    _check_bias(bias, n_q_heads)
     _check(_lib().llmrs_scored_prefill(
         _ptr(q), _LL(_row_stride(q, "q")), _ptr(out), _LL(_row_stride(out, "out")), _ptr(cache), _ptr(tiles), n_tiles,
         _ptr(ctx.q_start), _ptr(ctx.n_new), _ptr(ctx.cached_len), _ptr(table), table.size(1), n_q_heads, n_kv_heads,
-        dk, dv, page_size, ctypes.c_float(scale), ctypes.c_float(softcap), _ptr(sink), mask, mask_size,
-        dtype_code(q.dtype), q.size(0), cache.size(0), int(prefer_tc), _stream()), "scored_prefill")
+        dk, dv, page_size, ctypes.c_float(scale), ctypes.c_float(softcap), _ptr(sink), mask, mask_size, _ptr(bias),
+        0 if bias is None else bias.size(0), ctypes.c_float(out_scale), dtype_code(q.dtype), q.size(0), cache.size(0),
+        int(prefer_tc), _stream()), "scored_prefill")
+
+
+def _check_bias(bias: Optional[torch.Tensor], n_q_heads: int) -> None:
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.dim() != 2 or bias.size(1) != n_q_heads or bias.size(0) < 1:
+            raise KernelError(f"a distance bias of shape {tuple(bias.shape)} for {n_q_heads} query heads")
 
 
 def scored_decode_group(n_q_heads: int, n_kv_heads: int, dk: int, dv: int, page_size: int, dtype: torch.dtype) -> int:
@@ -1163,8 +1183,10 @@ def scored_decode_group(n_q_heads: int, n_kv_heads: int, dk: int, dv: int, page_
 
 def scored_decode(q, out, cache, dec_reqs, n_dec: int, ctx, table, max_splits: int, split_keys: int, n_q_heads: int,
                   n_kv_heads: int, dk: int, dv: int, page_size: int, scale: float, softcap: float, sink, mask: int,
-                  mask_size: int) -> None:
-    """Requests that bring one token: runs of ``split_keys`` keys from each request's first visible key."""
+                  mask_size: int, bias: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> None:
+    """Requests that bring one token: runs of ``split_keys`` keys from each request's first visible key. ``bias`` and
+    ``out_scale`` as in ``scored_prefill``."""
+    _check_bias(bias, n_q_heads)
     _need(q, "q", contiguous=False)
     _need(out, "out", q.dtype, contiguous=False)
     _need(cache, "cache", q.dtype)
@@ -1174,7 +1196,8 @@ def scored_decode(q, out, cache, dec_reqs, n_dec: int, ctx, table, max_splits: i
         _ptr(q), _LL(_row_stride(q, "q")), _ptr(out), _LL(_row_stride(out, "out")), _ptr(cache), _ptr(dec_reqs), n_dec,
         _ptr(ctx.q_start), _ptr(ctx.cached_len), _ptr(table), table.size(1), _ptr(scratch), max_splits, split_keys,
         n_q_heads, n_kv_heads, dk, dv, page_size, ctypes.c_float(scale), ctypes.c_float(softcap), _ptr(sink), mask,
-        mask_size, dtype_code(q.dtype), _stream()), "scored_decode", 2)
+        mask_size, _ptr(bias), 0 if bias is None else bias.size(0), ctypes.c_float(out_scale), dtype_code(q.dtype),
+        _stream()), "scored_decode", 2)
 
 
 # -- learned routers ----------------------------------------------------------------------------------------
@@ -1294,4 +1317,135 @@ def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Ten
     out = torch.empty(tuple(x.shape), dtype=x.dtype, device=x.device)
     _check(_lib().llmrs_rmsnorm_rows(_ptr(x), _LL(_row_stride(x, "x")), dtype_code(x.dtype), _ptr(weight), _ptr(out),
                                      x.size(0), x.size(1), ctypes.c_float(eps), _stream()), "rmsnorm_rows")
+    return out
+
+
+# -- hyper-connections, the pair-table embedding, PolyNorm, the gated delta rule ----------------------------------------
+HYPER_MAX_STREAMS = 8
+
+
+def hyper_step(x: torch.Tensor, write=None, read=None, eps: float = 0.0, act_dtype: torch.dtype = torch.float32):
+    """One pass over the streams ``x`` (float32 [tokens, streams * width], a token's streams side by side): with
+    ``write`` = (y, mix, out) every stream becomes ``sum_s mix[s, t] x_s + out[t] y`` (in place; ``y`` [tokens, width]
+    in float32 or the activation type, ``mix`` [streams, streams] and ``out`` [streams] float32 on the device); with
+    ``read`` = (in_w, g) the normed ``u = sum_s in_w[s] x_s`` of the streams as they are AFTER the write is returned,
+    ``u / sqrt(mean(u^2) + eps) * g`` with ``g`` one float32 on the device, rounded to ``act_dtype``."""
+    _need(x, "x", torch.float32)
+    y, mix, out = write if write is not None else (None, None, None)
+    in_w, g = read if read is not None else (None, None)
+    S = (mix.size(0) if mix is not None else in_w.numel())
+    n, width = x.size(0), x.size(1) // S
+    if x.size(1) != S * width or (y is not None and tuple(y.shape) != (n, width)):
+        raise KernelError(f"hyper_step: x {tuple(x.shape)} for {S} streams, y {None if y is None else tuple(y.shape)}")
+    for name, t, numel in (("mix", mix, S * S), ("out", out, S), ("in", in_w, S), ("g", g, 1)):
+        if t is not None:
+            _need(t, name, torch.float32)
+            if t.numel() != numel:
+                raise KernelError(f"hyper_step: {name} has {t.numel()} elements, expected {numel}")
+    if y is not None:
+        _need(y, "y")
+    u = torch.empty((n, width), dtype=act_dtype, device=x.device) if read is not None else None
+    _check(_lib().llmrs_hyper_step(_ptr(x), _ptr(y), 0 if y is None else dtype_code(y.dtype), _ptr(mix), _ptr(out),
+                                   _ptr(in_w), _ptr(g), _ptr(u), dtype_code(act_dtype), n, S, width,
+                                   ctypes.c_float(eps), _stream()), "hyper_step")
+    return u
+
+
+def hyper_leave(x: torch.Tensor, streams: int, write=None, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The sum of the streams of the given rows (int32 indices; None: all) as float32 [rows, width], taken after the
+    pending ``write`` = (y, mix, out) when there is one; ``x`` is not changed."""
+    _need(x, "x", torch.float32)
+    y, mix, out = write if write is not None else (None, None, None)
+    n, width = x.size(0), x.size(1) // streams
+    n_rows = n if rows is None else rows.numel()
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    if y is not None:
+        _need(y, "y")
+        _need(mix, "mix", torch.float32)
+        _need(out, "out", torch.float32)
+    total = torch.empty((n_rows, width), dtype=torch.float32, device=x.device)
+    _check(_lib().llmrs_hyper_leave(_ptr(x), _ptr(y), 0 if y is None else dtype_code(y.dtype), _ptr(mix), _ptr(out),
+                                    _ptr(rows), _ptr(total), n_rows, streams, width, _stream()), "hyper_leave")
+    return total
+
+
+def scaled_sum(a: torch.Tensor, b: torch.Tensor, sa: float, sb: float) -> torch.Tensor:
+    """``a * sa + b * sb`` in float32."""
+    _need(a, "a", torch.float32)
+    _need(b, "b", torch.float32)
+    if a.shape != b.shape:
+        raise KernelError(f"scaled_sum: {tuple(a.shape)} and {tuple(b.shape)}")
+    out = torch.empty_like(a)
+    _check(_lib().llmrs_scaled_sum(_ptr(a), _ptr(b), _ptr(out), _LL(a.numel()), ctypes.c_float(sa), ctypes.c_float(sb),
+                                   _stream()), "scaled_sum")
+    return out
+
+
+def bigram_embedding(table: torch.Tensor, pairs: Optional[torch.Tensor], ctx, prev_state: Optional[torch.Tensor],
+                     copies: int, scale: float, buckets: int, mul_prev: int, mul_cur: int) -> torch.Tensor:
+    """``table[id] * scale + pairs[(previous id * mul_prev + id * mul_cur) mod buckets]`` (row ``buckets`` for a
+    sequence's first token) as float32 [tokens, copies * hidden], the same row ``copies`` times. ``prev_state``
+    (float32 [slots, 1]) keeps every request's last token between steps. ``pairs`` None: the scaled table alone."""
+    _need(table, "table")
+    vocab, hidden = table.shape
+    n = ctx.token_ids.numel()
+    if pairs is not None:
+        _need(pairs, "pairs", table.dtype)
+        _need(prev_state, "prev_state", torch.float32)
+        if tuple(pairs.shape) != (buckets + 1, hidden):
+            raise KernelError(f"bigram_embedding: the pair table is {tuple(pairs.shape)}, expected {(buckets + 1, hidden)}")
+    out = torch.empty((n, copies * hidden), dtype=torch.float32, device=table.device)
+    _check(_lib().llmrs_bigram_embedding(
+        _ptr(table), _ptr(pairs), dtype_code(table.dtype), _ptr(ctx.token_ids), _ptr(ctx.token_req), _ptr(ctx.q_start),
+        _ptr(ctx.n_new), _ptr(ctx.cached_len), _ptr(ctx.slot_ids), _ptr(prev_state), _ptr(out), n, hidden, vocab,
+        copies, ctypes.c_float(scale), buckets, _LL(mul_prev), _LL(mul_cur), _stream()), "bigram_embedding")
+    return out
+
+
+def poly_norm(z: torch.Tensor, coeff: torch.Tensor, eps: float) -> torch.Tensor:
+    """``a N(z) + b N(z^2) + c N(z^3) + e`` row by row, N the division by the root mean square; ``coeff`` float32 [4]."""
+    _need(z, "z")
+    _need(coeff, "coeff", torch.float32)
+    if z.dim() != 2 or coeff.numel() != 4:
+        raise KernelError(f"poly_norm: z {tuple(z.shape)}, {coeff.numel()} coefficients")
+    out = torch.empty_like(z)
+    _check(_lib().llmrs_poly_norm(_ptr(z), _ptr(coeff), _ptr(out), z.size(0), z.size(1), ctypes.c_float(eps),
+                                  dtype_code(z.dtype), _stream()), "poly_norm")
+    return out
+
+
+def gated_delta(x: torch.Tensor, gate: torch.Tensor, taps: torch.Tensor, ba: torch.Tensor, a_log: torch.Tensor,
+                dt_bias: torch.Tensor, norm_w: torch.Tensor, state: torch.Tensor, conv_state: torch.Tensor, ctx,
+                n_kv_heads: int, n_heads: int, dk: int, dv: int, key_eps: float, q_scale: float, norm_eps: float,
+                out: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> torch.Tensor:
+    """The gated delta rule of ``csrc/gated_delta.cu`` over a step's tokens. ``x``: the q | k | v channels that enter
+    the short convolutions, a column slice with dense rows; ``gate``: [tokens, heads * dv] likewise; ``taps`` float32
+    [channels, K]; ``ba`` float32 [tokens, 2 * heads] (write strength, then decay projection); ``state`` float32
+    [slots, heads, dk, dv] and ``conv_state`` float32 [slots, K - 1, channels], both updated in place. Returns
+    [tokens, heads * dv] in the activation type (``out``: a view to write into), multiplied by ``out_scale``."""
+    C = 2 * n_kv_heads * dk + n_heads * dv
+    K = taps.size(1)
+    _need(x, "x", contiguous=False)
+    _need(gate, "gate", x.dtype, contiguous=False)
+    for name, t in (("taps", taps), ("ba", ba), ("a_log", a_log), ("dt_bias", dt_bias), ("norm_w", norm_w),
+                    ("state", state), ("conv_state", conv_state)):
+        _need(t, name, torch.float32)
+    n = x.size(0)
+    if x.size(1) != C or tuple(taps.shape) != (C, K) or tuple(ba.shape) != (n, 2 * n_heads) or \
+            tuple(state.shape[1:]) != (n_heads, dk, dv) or tuple(conv_state.shape[1:]) != (max(K - 1, 0), C) or \
+            gate.size(1) != n_heads * dv or norm_w.numel() != dv:
+        raise KernelError(f"gated_delta: x {tuple(x.shape)}, taps {tuple(taps.shape)}, ba {tuple(ba.shape)}, state "
+                          f"{tuple(state.shape)}, conv_state {tuple(conv_state.shape)}, gate {tuple(gate.shape)}")
+    if out is None:
+        out = torch.empty((n, n_heads * dv), dtype=x.dtype, device=x.device)
+    _need(out, "out", x.dtype, contiguous=False)
+    work = torch.empty((int(_lib_ll("llmrs_gated_delta_work_floats")(n, n_kv_heads, n_heads, dk, dv)),),
+                       dtype=torch.float32, device=x.device)
+    _check(_lib().llmrs_gated_delta(
+        _ptr(x), _LL(_row_stride(x, "x")), _ptr(gate), _LL(_row_stride(gate, "gate")), dtype_code(x.dtype), _ptr(taps),
+        _ptr(ba), _ptr(a_log), _ptr(dt_bias), _ptr(norm_w), _ptr(state), _ptr(conv_state), _ptr(ctx.token_req),
+        _ptr(ctx.q_start), _ptr(ctx.n_new), _ptr(ctx.slot_ids), _ptr(work), _ptr(out), _LL(_row_stride(out, "out")), n,
+        ctx.n_requests, n_kv_heads, n_heads, dk, dv, K, ctypes.c_float(key_eps), ctypes.c_float(q_scale),
+        ctypes.c_float(norm_eps), ctypes.c_float(out_scale), _stream()), "gated_delta", 4)
     return out

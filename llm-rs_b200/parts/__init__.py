@@ -2,8 +2,8 @@
 from .spec import CacheNeed, LayerSpec, ModelSpec, PartSpec, RunStep, StateNeed, WeightSpec
 from .registry import build, kinds, register, unregister
 from .base import Block, FeedForward, Mixer, Norm, Part, Plan, PositionEncoding, Runtime, StepInfo
-from . import (norm, position, attention, latent_attention, scored_attention, delta_rule, recurrent, mlp, moe, block,
-               embedding)  # registers the built-in parts
+from . import (norm, position, attention, latent_attention, scored_attention, delta_rule, recurrent, parallel, mlp, moe,
+               block, embedding)  # registers the built-in parts
 from .linear import Linear
 from .model import DecoderModel
 

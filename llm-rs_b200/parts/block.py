@@ -1,6 +1,7 @@
 """Arrangements of a mixer and a feed-forward around the residual stream."""
 from __future__ import annotations
 
+import inspect
 import os
 
 import torch
@@ -253,3 +254,104 @@ class SandwichBlock(Block):
             x = nxt.forward(h, None)
         self.feed_forward_out_norm.add_normed(h, self.feed_forward.forward(x, ctx))
         return h, None
+
+
+class HyperPending:
+    """A branch output that a hyper-connected block has not written into the streams yet: ``y`` [tokens, width] with
+    the ``mix`` [streams, streams] and ``out`` [streams] of its write."""
+    __slots__ = ("y", "mix", "out")
+
+    def __init__(self, y, mix, out):
+        self.y, self.mix, self.out = y, mix, out
+
+    def write(self):
+        return (self.y, self.mix, self.out)
+
+
+@register("block", "hyper")
+class HyperBlock(Block):
+    """Hyper-connections around a pre-norm layer: the residual stream is ``streams`` copies ``x_1 .. x_S`` per token (all
+    equal to the embedding output at the start; ``h`` is float32 [tokens, streams * width], a token's streams side by
+    side). Sublayer q (1: the mixer, 2: the feed-forward) with its tensors ``in`` [S], ``out`` [S] and ``mix`` [S, S]
+    (indexed [from, to]):
+
+        u = sum_s in[s] x_s;   y = sublayer(norm(u));   x_t <- sum_s mix[s, t] x_s + out[t] y   (all t from the old x)
+
+    and the model reads the SUM of the streams at the end (``leave``). The write of one sublayer and the read and norm of
+    the next are one pass over the token's streams (``ops.hyper_step``), across layers too: the feed-forward's output
+    leaves the block unwritten (a ``HyperPending``); the last write of a model is folded into the sum of the streams of
+    the wanted rows. The norms must be ``rmsnorm`` parts with one number as weight (``scalar``). ``names`` gives the
+    scopes of the two sublayers' tensors after the layer's prefix. A layer may have no feed-forward. Everything but
+    the normed rows is float32. ``learned`` False: no such tensors, in = out = 1 and mix the identity; with one stream
+    that is the plain pre-norm layer ``x <- x + sublayer(norm(x))``."""
+
+    def __init__(self, layer: LayerSpec, streams: int, names=("hc1.", "hc2."), learned: bool = True, prefix: str = ""):
+        if not 1 <= streams <= ops.HYPER_MAX_STREAMS:
+            raise ValueError(f"{streams} streams: the kernels take 1 to {ops.HYPER_MAX_STREAMS}")
+        p = layer.prefix
+        self.streams, self.learned = int(streams), bool(learned)
+        self.mixer_norm = build("norm", layer.mixer_norm, prefix=p)
+        self.mixer = build("mixer", layer.mixer, prefix=p + layer.mixer_scope)
+        self.feed_forward = self.feed_forward_norm = None
+        if layer.feed_forward is not None:
+            self.feed_forward_norm = build("norm", layer.feed_forward_norm, prefix=p)
+            self.feed_forward = build("feed_forward", layer.feed_forward, prefix=p + layer.feed_forward_scope)
+        for norm in (self.mixer_norm, self.feed_forward_norm):
+            if norm is not None and not getattr(norm, "scalar", False):
+                raise ValueError("a hyper-connected block takes norms with one number as weight (rmsnorm, scalar=True)")
+        self.scopes = [p + names[0]] + ([p + names[1]] if self.feed_forward is not None else [])
+        self.dim = self.mixer_norm.dim
+        self.hc = []
+
+    def parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward) if p is not None]
+
+    def chain(self):
+        return []
+
+    def weight_specs(self):
+        S = self.streams
+        specs = [s for part in self.parts() for s in part.weight_specs()]
+        for scope in self.scopes if self.learned else ():
+            specs += [WeightSpec(scope + "in", (S,), role="norm"), WeightSpec(scope + "out", (S,), role="norm"),
+                      WeightSpec(scope + "mix", (S, S), role="identity")]
+        return specs
+
+    def bind(self, tensors, runtime: Runtime):
+        self.act_dtype = runtime.act_dtype
+        for part in self.parts():
+            part.bind(tensors, runtime)
+        f32 = lambda name: tensors[name].to(torch.float32).contiguous()
+        if self.learned:
+            self.hc = [(f32(scope + "in"), f32(scope + "mix"), f32(scope + "out")) for scope in self.scopes]
+        else:
+            ones = torch.ones((self.streams,), dtype=torch.float32, device=runtime.device)
+            eye = torch.eye(self.streams, dtype=torch.float32, device=runtime.device)
+            self.hc = [(ones, eye, ones) for _ in self.scopes]
+
+    def _sublayer_out(self, part, x, *args):
+        """A sublayer's output, in float32 where the part can give it unrounded (its ``forward`` takes ``out_dtype``)."""
+        if "out_dtype" in inspect.signature(part.forward).parameters:
+            return part.forward(x, *args, out_dtype=torch.float32)
+        return part.forward(x, *args)
+
+    def forward(self, h, pending, ctx, cache):
+        if pending is not None and not isinstance(pending, HyperPending):
+            raise TypeError("a hyper-connected block follows a block that left a plain branch output unadded")
+        in1, mix1, out1 = self.hc[0]
+        norm1 = self.mixer_norm
+        x = ops.hyper_step(h, write=pending.write() if pending is not None else None, read=(in1, norm1.gain),
+                           eps=norm1.eps, act_dtype=self.act_dtype)
+        y = self._sublayer_out(self.mixer, x, ctx, cache)
+        if self.feed_forward is None:
+            return h, HyperPending(y, mix1, out1)
+        in2, mix2, out2 = self.hc[1]
+        norm2 = self.feed_forward_norm
+        x = ops.hyper_step(h, write=(y, mix1, out1), read=(in2, norm2.gain), eps=norm2.eps, act_dtype=self.act_dtype)
+        return h, HyperPending(self._sublayer_out(self.feed_forward, x, ctx), mix2, out2)
+
+    def leave(self, h, pending, rows):
+        """What the model's last norm reads: the sum of the streams of the given rows, float32 [rows, width]."""
+        if pending is not None and not isinstance(pending, HyperPending):
+            raise TypeError("a hyper-connected block cannot take a plain branch output")
+        return ops.hyper_leave(h, self.streams, write=pending.write() if pending is not None else None, rows=rows)

@@ -7,7 +7,7 @@ from .. import ops
 from .base import Part, Runtime
 from .linear import Linear
 from .registry import register
-from .spec import WeightSpec
+from .spec import StateNeed, WeightSpec
 
 
 @register("embedding", "token_embedding")
@@ -26,6 +26,48 @@ class TokenEmbedding(Part):
 
     def forward(self, token_ids):
         return ops.embedding(self.table, token_ids)
+
+
+@register("embedding", "pair_embedding")
+class PairEmbedding(Part):
+    """``h0[t] = table[id_t] * scale + pairs[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets]``: a token embedding
+    with a scale plus a hashed embedding of the token PAIR; a sequence's first token takes row number ``buckets`` (the
+    last row) of the pair table. The token before a step's first token of a request is per-request state (one number
+    per slot, kept by the cache manager with the first run-order entry's state), so a sequence may be cut anywhere and
+    decode steps replay from CUDA graphs. ``buckets`` 0: no pair table. The result is the float32 residual stream,
+    written ``streams`` times side by side for a model whose blocks keep several streams."""
+    STATE = "embedding.previous_token"
+    needs_context = True
+
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0, buckets: int = 0, mul_prev: int = 0,
+                 mul_cur: int = 0, streams: int = 1, name: str = "embedding.weight", pairs_name: str = "pairs",
+                 prefix: str = ""):
+        if buckets < 0 or mul_prev < 0 or mul_cur < 0 or streams < 1:
+            raise ValueError(f"pair embedding: buckets {buckets}, multipliers {mul_prev} / {mul_cur}, {streams} streams")
+        if vocab_size > 1 << 24:
+            raise ValueError(f"a vocabulary of {vocab_size} does not fit the previous token's float32 state")
+        self.vocab_size, self.hidden_size, self.scale = vocab_size, hidden_size, float(scale)
+        self.buckets, self.mul_prev, self.mul_cur, self.streams = int(buckets), int(mul_prev), int(mul_cur), int(streams)
+        self.name, self.pairs_name = prefix + name, prefix + pairs_name
+
+    def weight_specs(self):
+        specs = [WeightSpec(self.name, (self.vocab_size, self.hidden_size), role="embedding")]
+        if self.buckets:
+            specs.append(WeightSpec(self.pairs_name, (self.buckets + 1, self.hidden_size), role="embedding"))
+        return specs
+
+    def bind(self, tensors, runtime: Runtime):
+        self.table = tensors[self.name]
+        self.pairs = tensors[self.pairs_name] if self.buckets else None
+        if self.pairs is not None and self.pairs.dtype != self.table.dtype:
+            self.table, self.pairs = self.table.to(torch.float32), self.pairs.to(torch.float32)
+
+    def state_need(self):
+        return StateNeed({self.STATE: (1,)}) if self.buckets else None
+
+    def forward(self, ctx, state):
+        return ops.bigram_embedding(self.table, self.pairs, ctx, state.get(self.STATE) if self.buckets else None,
+                                    self.streams, self.scale, self.buckets, self.mul_prev, self.mul_cur)
 
 
 @register("lm_head", "linear_head")

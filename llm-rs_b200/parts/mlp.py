@@ -92,16 +92,19 @@ class SwiGLU(FeedForward):
 
 @register("feed_forward", "dense")
 class DenseFF(FeedForward):
-    """``down(act(up(x)))`` without a gate; ``activation`` "relu_sq" is the square of relu. ``names`` maps the roles
-    up and down to the tensors' names after the prefix."""
-    ROLES = ("up", "down")
-    ACTIVATIONS = ("relu_sq",)
+    """``down(act(up(x)))`` without a gate; ``activation`` "relu_sq" is the square of relu, "polynorm" is
+    ``a N(z) + b N(z^2) + c N(z^3) + e`` with powers taken element by element, N the division of a token's row by its
+    root mean square (``act_eps`` inside the root, float32 sums) and the four learned numbers in the tensor ``act``.
+    ``names`` maps the roles up, down and act to the tensors' names after the prefix."""
+    ROLES = ("up", "down", "act")
+    ACTIVATIONS = ("relu_sq", "polynorm")
 
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "relu_sq", names=None,
-                 prefix: str = ""):
+                 act_eps: float = 1e-6, prefix: str = ""):
         if activation not in self.ACTIVATIONS:
             raise ValueError(f"unknown activation {activation!r}; known: {self.ACTIVATIONS}")
         self.hidden_size, self.intermediate_size, self.activation = hidden_size, intermediate_size, activation
+        self.act_eps = float(act_eps)
         self.prefix = prefix
         self.names = {role: role for role in self.ROLES}
         self.names.update(names or {})
@@ -110,14 +113,21 @@ class DenseFF(FeedForward):
 
     def weight_specs(self):
         H, I = self.hidden_size, self.intermediate_size
-        return [WeightSpec(self.prefix + self.names["up"], (I, H)), WeightSpec(self.prefix + self.names["down"], (H, I))]
+        specs = [WeightSpec(self.prefix + self.names["up"], (I, H)), WeightSpec(self.prefix + self.names["down"], (H, I))]
+        if self.activation == "polynorm":
+            specs.append(WeightSpec(self.prefix + self.names["act"], (4,), role="norm"))
+        return specs
 
     def bind(self, tensors, runtime: Runtime):
         self.up = Linear(tensors[self.prefix + self.names["up"]], None, runtime.act_dtype)
         self.down = Linear(tensors[self.prefix + self.names["down"]], None, runtime.act_dtype)
+        if self.activation == "polynorm":
+            self.coeff = tensors[self.prefix + self.names["act"]].to(torch.float32).contiguous()
 
     def chain(self):
         return [self.up, self.down]
 
-    def forward(self, x, ctx):
-        return self.down.forward(ops.relu_sq(self.up.forward(x)))
+    def forward(self, x, ctx, out_dtype=None):
+        z = self.up.forward(x)
+        act = ops.poly_norm(z, self.coeff, self.act_eps) if self.activation == "polynorm" else ops.relu_sq(z)
+        return self.down.forward(act, out_dtype=out_dtype)

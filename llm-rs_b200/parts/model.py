@@ -49,9 +49,13 @@ class DecoderModel:
         An entry that reads another entry's cache wants no pages and no mixer state of its own (it sees the other
         entry's), but keeps its block's state."""
         needs = []
-        for step in self.spec.run_order:
+        # State that the embedding keeps per request (the token before a step's first) lives with the first entry's.
+        of_embedding = getattr(self.embedding, "state_need", lambda: None)()
+        for s, step in enumerate(self.spec.run_order):
             block = self.blocks[step.layer]
             own = getattr(block, "state_need", lambda: None)()       # state of the block itself (a token shift)
+            if s == 0 and of_embedding is not None:
+                own = StateNeed({**(own.tensors if own is not None else {}), **of_embedding.tensors})
             if step.cache_of is not None:
                 needs.append((None, own))
             else:
@@ -65,9 +69,12 @@ class DecoderModel:
     def forward(self, ctx) -> Optional[torch.Tensor]:
         """Run the step's tokens through every run-order entry; float32 logits of the
         wanted rows ([wanted, vocab]), or None when nothing is wanted."""
-        h = self.embedding.forward(ctx.token_ids)
-        pending = None
         order = self.spec.run_order
+        if getattr(self.embedding, "needs_context", False):      # an embedding that reads more of the step than the ids
+            h = self.embedding.forward(ctx, ctx.layer_cache(0).state if order else {})
+        else:
+            h = self.embedding.forward(ctx.token_ids)
+        pending = None
         # What the passes over a looped stretch take from the embedding output is the same in every pass: made once.
         entered = self.reentry.prepare(h, ctx) if self.reentry is not None else None
         for s, step in enumerate(order):
@@ -83,5 +90,10 @@ class DecoderModel:
                 h, pending = block.forward(h, pending, ctx, ctx.layer_cache(s))
         if ctx.n_want == 0:
             return None
-        x = self.final_norm.forward(h, pending, rows=ctx.want_rows)
+        last = self.blocks[order[-1].layer] if order else None
+        if hasattr(last, "leave"):
+            # A block that keeps the stream in a form of its own (several streams) hands over what the last norm reads.
+            x = self.final_norm.forward(last.leave(h, pending, ctx.want_rows), None)
+        else:
+            x = self.final_norm.forward(h, pending, rows=ctx.want_rows)
         return self.lm_head.forward(x)

@@ -89,6 +89,8 @@ class WeightSpec:
       "norm"       1 + N(0, norm_jitter); held as float32 (exact from bfloat16)
       "norm_offset" N(0, norm_jitter): a norm weight stored around zero; held as float32
       "bias"       ~N(0, sigma)
+      "identity"   a square matrix, the identity + N(0, norm_jitter); held as float32
+      "conv"       taps of a short convolution, ~N(0, 1/2)
       "int_table"  integers, held as int32
       "expert_table" int32 rows of different integers below ``limit`` (which experts a row uses)
     ``optional`` tensors may be absent from the folder. ``load=False`` marks a tensor that the folder

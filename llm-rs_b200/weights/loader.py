@@ -42,7 +42,7 @@ def _target_dtype(spec: WeightSpec, stored: torch.dtype, act_dtype: torch.dtype)
         return torch.int32 if not stored.is_floating_point and stored != torch.bool else None
     if not stored.is_floating_point:
         return None
-    if spec.role in ("norm", "norm_offset") or act_dtype == torch.float32 or stored in (torch.float32, torch.float64):
+    if spec.role in ("norm", "norm_offset", "identity") or act_dtype == torch.float32 or stored in (torch.float32, torch.float64):
         return torch.float32
     return torch.bfloat16
 

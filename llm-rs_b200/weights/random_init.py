@@ -32,6 +32,11 @@ def _make(spec: WeightSpec, seed: int, index: int, sigma: float, norm_jitter: fl
         t = norm_jitter * torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
     elif spec.role == "norm":
         t = 1.0 + norm_jitter * torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
+    elif spec.role == "identity":
+        t = torch.eye(spec.shape[0], spec.shape[1], dtype=torch.float32, device=device) + \
+            norm_jitter * torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
+    elif spec.role == "conv":
+        t = 0.5 * torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
     else:
         t = torch.empty(spec.shape, dtype=dtype, device=device)
         rows = spec.shape[0] if len(spec.shape) > 1 else 1
@@ -53,7 +58,7 @@ def random_tensors(specs: Sequence[WeightSpec], seed: int, sigma: float = 0.02, 
                    ) -> Dict[str, torch.Tensor]:
     out = {}
     for index, spec in enumerate(sorted((s for s in specs if s.load), key=lambda s: s.name)):
-        dt = (norm_dtype or dtype) if spec.role in ("norm", "norm_offset") else dtype
+        dt = (norm_dtype or dtype) if spec.role in ("norm", "norm_offset", "identity") else dtype
         out[spec.name] = _make(spec, seed, index, sigma, norm_jitter, dt, device)
     return out
 
