@@ -206,7 +206,8 @@ class FekolornConfig:
                 mlp = DenseMLP(_get(mlp_raw, "ff", int, where, 1))
             layers.append(FekolornLayer(lr["type"], mixer, mlp))
         # Layers whose values are mixed must agree on the values' shape with the first of them.
-        mixed = [l.mixer for l in layers if isinstance(l.mixer, SoftmaxMixer) and l.mixer.v_mix]
+        softmax = [l.mixer if isinstance(l.mixer, SoftmaxMixer) else l.mixer.left for l in layers]
+        mixed = [m for m in softmax if m.v_mix]
         for m in mixed[1:]:
             if (m.kv_heads, m.vdim) != (mixed[0].kv_heads, mixed[0].vdim):
                 raise ConfigError("config: layers with v_mix must have the first such layer's kv_heads and vdim")

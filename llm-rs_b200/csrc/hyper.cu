@@ -13,13 +13,14 @@
 //   scaled_sum    out = a * sa + b * sb, float32 (two branches that run side by side)
 #include "common.cuh"
 
-constexpr int HY_MAXS = 8, HY_THREADS = 256;
+constexpr int HY_MAXS = 16, HY_THREADS = 256;
 
 struct HyperParams {
   float mix[HY_MAXS][HY_MAXS], out[HY_MAXS], in[HY_MAXS];
 };
 
-template <typename TY, typename TA>
+// SMAX: the streams the unrolled loops are built for (the next of 2, 4, 8, 16 at or above S).
+template <typename TY, typename TA, int SMAX>
 __global__ void __launch_bounds__(HY_THREADS)
 hyper_step_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ mix,
                   const float* __restrict__ out, const float* __restrict__ in_next, const float* __restrict__ g_next,
@@ -37,27 +38,27 @@ hyper_step_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* 
   float* xt = x + (size_t)t * S * width;
   float ss = 0.f;
   for (int c = threadIdx.x; c < width; c += HY_THREADS) {
-    float xs[HY_MAXS];
+    float xs[SMAX];
 #pragma unroll
-    for (int s = 0; s < HY_MAXS; ++s) xs[s] = s < S ? xt[(size_t)s * width + c] : 0.f;
+    for (int s = 0; s < SMAX; ++s) xs[s] = s < S ? xt[(size_t)s * width + c] : 0.f;
     if (y) {
       const float yv = to_float(y[(size_t)t * width + c]);
-      float nx[HY_MAXS];
+      float nx[SMAX];
 #pragma unroll
-      for (int r = 0; r < HY_MAXS; ++r) {
+      for (int r = 0; r < SMAX; ++r) {
         float a = p.out[r] * yv;
 #pragma unroll
-        for (int s = 0; s < HY_MAXS; ++s) a = fmaf(p.mix[s][r], xs[s], a);
+        for (int s = 0; s < SMAX; ++s) a = fmaf(p.mix[s][r], xs[s], a);
         nx[r] = a;
       }
 #pragma unroll
-      for (int r = 0; r < HY_MAXS; ++r)
+      for (int r = 0; r < SMAX; ++r)
         if (r < S) xt[(size_t)r * width + c] = xs[r] = nx[r];
     }
     if (in_next) {
       float u = 0.f;
 #pragma unroll
-      for (int s = 0; s < HY_MAXS; ++s) u = fmaf(p.in[s], xs[s], u);
+      for (int s = 0; s < SMAX; ++s) u = fmaf(p.in[s], xs[s], u);
       u_row[c] = u;
       ss = fmaf(u, u, ss);
     }
@@ -80,17 +81,24 @@ LLMRS_API int llmrs_hyper_step(float* x, const void* y, int y_dtype, const float
   LLMRS_REQUIRE(width <= 48 * 1024, "hyper_step: width %d is too large", width);
   if (n_tokens == 0) return 0;
   const size_t smem = in_next ? (size_t)width * sizeof(float) : 0;
-#define LLMRS_HY_LAUNCH(TY, TA)                                                                                   \
-  do {                                                                                                            \
-    static size_t configured = 40 * 1024;                                                                         \
-    if (smem > configured) {                                                                                      \
-      cudaError_t e = cudaFuncSetAttribute(hyper_step_kernel<TY, TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                           (int)smem);                                                            \
-      if (e != cudaSuccess) return llmrs_fail("hyper_step: shared memory %zu: %s", smem, cudaGetErrorString(e));  \
-      configured = smem;                                                                                          \
-    }                                                                                                             \
-    hyper_step_kernel<TY, TA><<<n_tokens, HY_THREADS, smem, stream>>>(x, (const TY*)y, mix, out, in_next, g_next, \
-                                                                      (TA*)u_out, S, width, eps);                 \
+#define LLMRS_HY_LAUNCH_S(TY, TA, SMAX)                                                                              \
+  do {                                                                                                                 \
+    static size_t configured = 40 * 1024;                                                                              \
+    if (smem > configured) {                                                                                           \
+      cudaError_t e = cudaFuncSetAttribute(hyper_step_kernel<TY, TA, SMAX>,                                            \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                    \
+      if (e != cudaSuccess) return llmrs_fail("hyper_step: shared memory %zu: %s", smem, cudaGetErrorString(e));       \
+      configured = smem;                                                                                               \
+    }                                                                                                                  \
+    hyper_step_kernel<TY, TA, SMAX><<<n_tokens, HY_THREADS, smem, stream>>>(x, (const TY*)y, mix, out, in_next, g_next, \
+                                                                            (TA*)u_out, S, width, eps);                \
+  } while (0)
+#define LLMRS_HY_LAUNCH(TY, TA)                     \
+  do {                                              \
+    if (S <= 2) LLMRS_HY_LAUNCH_S(TY, TA, 2);       \
+    else if (S <= 4) LLMRS_HY_LAUNCH_S(TY, TA, 4);  \
+    else if (S <= 8) LLMRS_HY_LAUNCH_S(TY, TA, 8);  \
+    else LLMRS_HY_LAUNCH_S(TY, TA, 16);             \
   } while (0)
   const bool y32 = y == nullptr || y_dtype == LLMRS_F32;
   if (!y32 && y_dtype != LLMRS_BF16) return llmrs_fail("hyper_step: unknown y dtype %d", y_dtype);
@@ -104,6 +112,7 @@ LLMRS_API int llmrs_hyper_step(float* x, const void* y, int y_dtype, const float
     return llmrs_fail("hyper_step: unknown dtype %d", act_dtype);
   }
 #undef LLMRS_HY_LAUNCH
+#undef LLMRS_HY_LAUNCH_S
   return llmrs_launch_status("hyper_step");
 }
 

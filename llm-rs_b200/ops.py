@@ -1321,7 +1321,7 @@ def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Ten
 
 
 # -- hyper-connections, the pair-table embedding, PolyNorm, the gated delta rule ----------------------------------------
-HYPER_MAX_STREAMS = 8
+HYPER_MAX_STREAMS = 16
 
 
 def hyper_step(x: torch.Tensor, write=None, read=None, eps: float = 0.0, act_dtype: torch.dtype = torch.float32):

@@ -73,6 +73,8 @@ class ScoredAttention(Mixer):
         if v_norm not in ("none", "head_unit") or v_mix not in ("none", "source", "mixed"):
             raise ValueError(f"v_norm {v_norm!r} (known: 'none', 'head_unit'), v_mix {v_mix!r} (known: 'none', 'source', "
                              "'mixed')")
+        if v_mix == "source" and v_norm != "none":
+            raise ValueError("a layer whose values are normed per head cannot be the source of mixed values")
         if bias_rows and (bias_rows < 2 or bias_max <= bias_rows // 2):
             raise ValueError(f"a distance bias of {bias_rows} rows reaching to {bias_max}: at least 2 rows, and the "
                              "reach beyond half of them")

@@ -104,7 +104,7 @@ def save_file(tensors: Dict[str, torch.Tensor], path: str) -> None:
         f.write(blob)
         for name in order:
             t = tensors[name].detach().contiguous().cpu()
-            f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")      # reshape: a tensor without axes too
     os.replace(tmp, path)
 
 

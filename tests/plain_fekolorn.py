@@ -158,10 +158,12 @@ def gated_delta(h, m, w, p, eps):
     return out @ w[p + "o"].T
 
 
-def parallel_mixer(h, m, w, p, eps, positions):
-    left, _ = softmax_mixer(h, m["left"], w, p + "left.", eps, positions, whole_norm=False, value_norm=True)
+def parallel_mixer(h, m, w, p, eps, positions, v_first=None):
+    """(weighted sum of the two sides, the softmax side's values as cached)."""
+    left, cached = softmax_mixer(h, m["left"], w, p + "left.", eps, positions, whole_norm=False, value_norm=True,
+                                 v_first=v_first)
     right = gated_delta(h, m["right"], w, p + "right.", eps)
-    return float(m["left_scale"]) * left + float(m["right_scale"]) * right
+    return float(m["left_scale"]) * left + float(m["right_scale"]) * right, cached
 
 
 def poly_norm(z, coeff, eps):
@@ -198,19 +200,23 @@ def forward(tokens, cfg, w, residuals=None):
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
         m = layer["mixer"]
+        kept = {}
         if layer["type"] == "parallel":
-            fn = lambda h: parallel_mixer(h, m, w, p + "mix.", eps, positions)
-        else:
-            kept = {}
+            softmax = m["left"]
 
-            def fn(h, kept=kept):
-                o, cached = softmax_mixer(h, m, w, p + "mix.", eps, positions, whole_norm=True, value_norm=False,
-                                          v_first=v_first)
-                kept["v"] = cached
+            def fn(h, kept=kept, m=m):
+                o, kept["v"] = parallel_mixer(h, m, w, p + "mix.", eps, positions, v_first=v_first)
+                return o
+        else:
+            softmax = m
+
+            def fn(h, kept=kept, m=m):
+                o, kept["v"] = softmax_mixer(h, m, w, p + "mix.", eps, positions, whole_norm=True, value_norm=False,
+                                             v_first=v_first)
                 return o
         streams = sublayer(streams, fn, w[p + "norm1"], eps, w, p + "hc1.")
-        if layer["type"] != "parallel" and m.get("v_mix") and v_first is None:
-            v_first = kept["v"]
+        if softmax.get("v_mix") and v_first is None:
+            v_first = kept["v"]      # the first such layer's values, which it keeps unmixed
         if layer.get("mlp") is not None:
             f = layer["mlp"]
             streams = sublayer(streams, lambda h: feed_forward(h, f, w, p + "mlp.", eps), w[p + "norm2"], eps, w,
