@@ -20,7 +20,8 @@ A "step" is one decode step of the whole batch. The default is batch 8 at a cont
 The K timed steps run back to back as five runs of K/5 steps with a CUDA event between them: ``value`` and
 ``ms_per_step`` are the median run's, ``repeats`` gives the runs' spread and the mean over all K steps.
 ``--workload rusadra`` measures the Rusadra design beside Qwen3 at equal size instead (see DESIGN_SIZES below), and
-``--workload pusazen`` the Pusazen design beside Rusadra, ``--workload pozelix`` the Pozelix design beside both; the
+``--workload pusazen`` the Pusazen design beside Rusadra, ``--workload pozelix`` the Pozelix design beside both,
+``--workload fekolorn`` the Fekolorn design beside Pusazen and Rusadra; the
 default workload and its JSON line are unchanged by them.
 Fractions are given against two denominators: the peaks measured on this pool (MEASURED_PEAKS.json beside
 this file when present, else 6.65 TB/s and 1.59 PFLOP/s) and the nominal figures of the part (7.7 TB/s,
@@ -131,6 +132,31 @@ def pozelix_configs(z):
            "layers": [dict(window if i % 2 == 0 else latent, mlp=moe if i % 2 == 0 else dense)
                       for i in range(z["layers"] - twice)]}
     return poz, design_configs(z)[0], pusazen_configs(z)[0]
+
+
+# ``--workload fekolorn``: the Fekolorn design (four residual streams with learned connections; layers in turn a parallel
+# mixer, softmax attention over every earlier key beside a gated delta rule behind short convolutions, and attention
+# through a sliding window with a bias per distance bucket and values mixed with the first such layer's; a dense
+# feed-forward with the PolyNorm activation; an embedding with a table of token pairs) beside the Pusazen design
+# (attention with options on the score: the same part and kernels; a recurrence with a matrix state) and the Rusadra
+# design (the generalized delta rule: the like of the gated one) at equal width, depth, vocabulary and active
+# feed-forward width; the same measurements.
+def fekolorn_configs(z):
+    """(Fekolorn config.json, Pusazen config.json, Rusadra config.json) of one entry of DESIGN_SIZES."""
+    kv = max(1, z["heads"] // 4)
+    left = {"heads": z["heads"], "kv_heads": kv, "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+            "rot": {"base": 1e6, "dims": z["rot"]}}
+    right = {"heads": z["delta_heads"] // 2, "kv_heads": z["delta_heads"] // 4, "dim": 2 * z["delta_dim"],
+             "vdim": 2 * z["delta_dim"], "conv": 4}
+    parallel = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.8, "right_scale": 0.9}}
+    attention = {"type": "attention", "mixer": {
+        "heads": z["heads"], "kv_heads": kv, "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+        "mask": {"size": z["window"]}, "bias_max": z["window"], "bias_rows": 32, "v_mix": True}}
+    mlp = {"kind": "dense", "ff": z["top"] * z["ff"]}
+    fek = {"architecture": "Fekolorn", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "streams": 4,
+           "embedding": {"scale": 0.5, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+           "layers": [dict(parallel if i % 2 == 0 else attention, mlp=mlp) for i in range(z["layers"])]}
+    return fek, pusazen_configs(z)[0], design_configs(z)[0]
 
 
 def run_design(args, configs=None, workload="rusadra"):
@@ -424,13 +450,14 @@ def main():
     ap.add_argument("--profile", action="store_true", help="instead of the benchmark: time every kernel class of one "
                     "decode step and of the prefill with CUDA events (eager launches, NVTX ranges) and print a table "
                     "with bytes, flops and the fraction of the peaks to standard error, the rows as JSON to standard output")
-    ap.add_argument("--workload", default="decode", choices=["decode", *WORKLOADS, "rusadra", "pusazen", "pozelix"],
+    ap.add_argument("--workload", default="decode", choices=["decode", *WORKLOADS, "rusadra", "pusazen", "pozelix", "fekolorn"],
                     help="decode: the benchmark contract (default). mixed14b / stress32b: a whole serving run "
                     "through the engine on the layer sizes of Qwen3-14B / Qwen3-32B. rusadra: prefill and decode of the "
                     "Rusadra design beside Qwen3 at equal width, depth, vocabulary and active feed-forward width, with "
                     "every kernel class's fraction of the device's peaks. pusazen: the same for the Pusazen design "
                     "beside Rusadra at equal width, depth, vocabulary, experts and expert width. pozelix: the same "
-                    "for the Pozelix design beside Rusadra and Pusazen")
+                    "for the Pozelix design beside Rusadra and Pusazen. fekolorn: the same for the Fekolorn design beside "
+                    "Pusazen and Rusadra")
     ap.add_argument("--pool-tokens", type=int, default=0, help="size of the cache pool of a --workload run in "
                     "tokens (default: what holds every request whole); smaller makes the scheduler preempt")
     args = ap.parse_args()
@@ -447,6 +474,8 @@ def main():
         return run_design(args, pusazen_configs, "pusazen")
     if args.workload == "pozelix":
         return run_design(args, pozelix_configs, "pozelix")
+    if args.workload == "fekolorn":
+        return run_design(args, fekolorn_configs, "fekolorn")
     if args.workload == "rusadra":
         return run_design(args)
     if args.workload != "decode":

@@ -637,7 +637,8 @@ int llmrs_attn_prefill_tc_scored(const void* q, long long q_stride, int n_tokens
                                  const void* cache, long long cache_rows, const int* tiles, int n_tiles,
                                  const int* q_start, const int* n_new, const int* cached_len, const int* block_table,
                                  int table_stride, int n_q_heads, int n_kv_heads, int page_size, int window, float scale,
-                                 float softcap, const float* sink, int chunk, int* error_flag, cudaStream_t stream);
+                                 float softcap, const float* sink, int chunk, float out_scale, int* error_flag,
+                                 cudaStream_t stream);
 
 static int g_scored_generic_only = 0;
 // 1: bfloat16 also takes the kernel for any type (tests compare the two).
@@ -670,14 +671,14 @@ LLMRS_API int llmrs_scored_prefill(const void* q, long long q_stride, void* out,
   // memory), with the cap, the sink and the mask in its softmax threads. Its waits are bounded; a block that gives
   // up leaves a code that llmrs_attention_tc_error reads.
   if (dtype == LLMRS_BF16 && prefer_tc && !g_scored_generic_only && dk == 128 && dv == 128 && n_tiles <= 8192 &&
-      bias == nullptr && out_scale == 1.0f &&
+      bias == nullptr &&
       out_stride % 8 == 0 && ((uintptr_t)out & 15) == 0 &&
       llmrs_attn_prefill_tc_supported(q, q_stride, cache, dk, page_size, scale))
     return llmrs_attn_prefill_tc_scored(q, q_stride, n_tokens, out, out_stride, cache,
                                         (long long)n_pages * n_kv_heads * 2 * page_size, tiles, n_tiles, q_start, n_new,
                                         cached_len, block_table, table_stride, n_q_heads, n_kv_heads, page_size,
                                         mask == MASK_WINDOW ? mask_size : 0, scale, softcap, sink,
-                                        mask == MASK_CHUNK ? mask_size : 0, nullptr, stream);
+                                        mask == MASK_CHUNK ? mask_size : 0, out_scale, nullptr, stream);
   if (dtype == LLMRS_BF16 && !g_scored_generic_only && q_stride % 2 == 0 && out_stride % 2 == 0) {
 #define LLMRS_SM_CASE(K, V)                                                                                     \
   if (dk == 16 * K && dv == 16 * V)                                                                              \

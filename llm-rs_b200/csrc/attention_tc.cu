@@ -207,8 +207,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
                        const int* __restrict__ q_start, const int* __restrict__ n_new,
                        const int* __restrict__ cached_len, const int* __restrict__ block_table, int table_stride,
                        int n_list, int persistent, int n_q_heads, int n_kv_heads, int page_size, int box_rows, int window, float scale,
-                       float softcap_, const float* __restrict__ sink_, int chunk_,
+                       float softcap_, const float* __restrict__ sink_, int chunk_, float out_scale_,
                        int* __restrict__ error_flag, uint32_t wait_limit, int test_skip_tile) {
+  const float out_scale = SCORED ? out_scale_ : 1.0f;      // the output is multiplied by it
   const float softcap = SCORED ? softcap_ : 0.f;
   const float* sink = SCORED ? sink_ : nullptr;
   const int chunk = SCORED ? chunk_ : 0;
@@ -567,7 +568,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
         // Every thread reads its row of O (the load is warp-wide); rows past the portion's end are not stored.
         // A sink is one more term of the denominator, with no key and no value, against the same reference.
         if (sink != nullptr && m_ref != -INFINITY) l_sum += ex2(fminf(sink[it.head] * AT_LOG2E - m_ref, 126.0f));
-        const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
+        const float inv = l_sum > 0.f ? out_scale / l_sum : 0.f;
         bf16* orow = out + (size_t)(it.tok0 + row) * out_stride + (size_t)it.head * AT_D;
 #pragma unroll 1
         for (int c = 0; c < AT_D; c += 32) {
@@ -674,12 +675,14 @@ bool llmrs_attn_prefill_tc_supported(const void* q, long long q_stride, const vo
 // Prefill attention on tcgen05 (see the head of this file). `n_tokens` is the number of rows of q,
 // `cache_rows` = n_pages * n_kv_heads * 2 * page_size the number of head_dim-wide rows of the cache.
 // With options on the score (softcap > 0: cap * tanh(score / cap); sink: one number per query head in the softmax's
-// denominator, or null; chunk > 0: a query sees the keys of its own chunk of that many positions only).
+// denominator, or null; chunk > 0: a query sees the keys of its own chunk of that many positions only; out_scale
+// multiplies the output).
 int llmrs_attn_prefill_tc_scored(const void* q, long long q_stride, int n_tokens, void* out, long long out_stride,
                                  const void* cache, long long cache_rows, const int* tiles, int n_tiles,
                                  const int* q_start, const int* n_new, const int* cached_len, const int* block_table,
                                  int table_stride, int n_q_heads, int n_kv_heads, int page_size, int window, float scale,
-                                 float softcap, const float* sink, int chunk, int* error_flag, cudaStream_t stream);
+                                 float softcap, const float* sink, int chunk, float out_scale, int* error_flag,
+                                 cudaStream_t stream);
 
 int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void* out, long long out_stride,
                           const void* cache, long long cache_rows, const int* tiles, int n_tiles, const int* q_start,
@@ -688,14 +691,15 @@ int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void*
                           cudaStream_t stream) {
   return llmrs_attn_prefill_tc_scored(q, q_stride, n_tokens, out, out_stride, cache, cache_rows, tiles, n_tiles, q_start,
                                       n_new, cached_len, block_table, table_stride, n_q_heads, n_kv_heads, page_size,
-                                      window, scale, 0.f, nullptr, 0, error_flag, stream);
+                                      window, scale, 0.f, nullptr, 0, 1.0f, error_flag, stream);
 }
 
 int llmrs_attn_prefill_tc_scored(const void* q, long long q_stride, int n_tokens, void* out, long long out_stride,
                                  const void* cache, long long cache_rows, const int* tiles, int n_tiles,
                                  const int* q_start, const int* n_new, const int* cached_len, const int* block_table,
                                  int table_stride, int n_q_heads, int n_kv_heads, int page_size, int window, float scale,
-                                 float softcap, const float* sink, int chunk, int* error_flag, cudaStream_t stream) {
+                                 float softcap, const float* sink, int chunk, float out_scale, int* error_flag,
+                                 cudaStream_t stream) {
   CUtensorMap map_kv;
   int rc;
   (void)n_tokens;
@@ -703,7 +707,7 @@ int llmrs_attn_prefill_tc_scored(const void* q, long long q_stride, int n_tokens
   const int box_rows = page_size % 64 == 0 ? 64 : 16;
   if ((rc = make_map(&map_kv, cache, cache_rows, AT_D, AT_D, box_rows))) return rc;
   const size_t smem = AT_STAGES * STAGE_BYTES + (4 * AT_STAGES + 8) * 8 + 16 + 2 * AT_MAX_LIST;
-  const bool scored = softcap > 0.f || sink != nullptr || chunk > 0;
+  const bool scored = softcap > 0.f || sink != nullptr || chunk > 0 || out_scale != 1.0f;
   static bool configured[2] = {false, false};
   if (!configured[scored]) {
     cudaError_t e = scored ? cudaFuncSetAttribute(attn_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
@@ -731,11 +735,11 @@ int llmrs_attn_prefill_tc_scored(const void* q, long long q_stride, int n_tokens
     attn_prefill_tc_kernel<true><<<grid, AT_THREADS + 96, smem, stream>>>(
         map_kv, (const bf16*)q, q_stride, (bf16*)out, out_stride, tiles, q_start, n_new, cached_len, block_table,
         table_stride, n_tiles, persistent, n_q_heads, n_kv_heads, page_size, box_rows, window, scale, softcap, sink, chunk,
-        error_flag, g_wait_limit, g_test_skip_tile);
+        out_scale, error_flag, g_wait_limit, g_test_skip_tile);
   else
     attn_prefill_tc_kernel<false><<<grid, AT_THREADS + 96, smem, stream>>>(
         map_kv, (const bf16*)q, q_stride, (bf16*)out, out_stride, tiles, q_start, n_new, cached_len, block_table,
         table_stride, n_tiles, persistent, n_q_heads, n_kv_heads, page_size, box_rows, window, scale, 0.f, nullptr, 0,
-        error_flag, g_wait_limit, g_test_skip_tile);
+        1.0f, error_flag, g_wait_limit, g_test_skip_tile);
   return llmrs_launch_status("attn_prefill_tc");
 }

@@ -149,7 +149,35 @@ def _cost_scored_decode(q, out, cache, dec_reqs, n_dec, ctx, table, max_splits, 
             lambda: 2.0 * float(keys) * n_q_heads * (dk + dv))
 
 
+def _cost_hyper_step(x, write=None, read=None, **k):
+    # The streams are read, and written when a branch output is added; that output is read, the normed row written.
+    n = _nbytes(x) * (2 if write is not None else 1)
+    if write is not None:
+        n += _nbytes(write[0])
+    if read is not None:
+        n += x.size(0) * (x.size(1) // read[0].numel()) * (2 if k.get("act_dtype") == torch.bfloat16 else 4)
+    return f"{'write ' if write is not None else ''}{'read' if read is not None else ''}".strip(), n, 0.0
+
+
+def _cost_hyper_leave(x, streams, write=None, rows=None, **k):
+    n_rows = x.size(0) if rows is None else rows.numel()
+    width = x.size(1) // streams
+    return "", n_rows * width * 4 * (streams + 1) + (n_rows * width * write[0].element_size() if write is not None else 0), 0.0
+
+
+def _cost_gated_delta(x, gate, taps, ba, a_log, dt_bias, norm_w, state, conv_state, ctx, n_kv_heads, n_heads, dk, dv,
+                      *a, **k):
+    # The convolutions' inputs and the gate are read, the output written; every request's state is read and written.
+    tokens, e = x.size(0), x.element_size()
+    return (f"{tokens} tokens", tokens * (x.size(1) + 2 * n_heads * dv) * e + 2 * ctx.n_requests * n_heads * dk * dv * 4,
+            7.0 * tokens * n_heads * dk * dv)
+
+
 WRAPPED: Dict[str, Callable] = {
+    "hyper_step": _cost_hyper_step, "hyper_leave": _cost_hyper_leave, "gated_delta": _cost_gated_delta,
+    "scaled_sum": lambda a, b, *r, **k: ("", 3 * _nbytes(a), 0.0), "poly_norm": _cost_rows(0),
+    "bigram_embedding": lambda table, pairs, ctx, prev, copies, *a, **k: (
+        "", ctx.token_ids.numel() * table.size(1) * ((1 if pairs is None else 2) * table.element_size() + 4 * copies), 0.0),
     "linear_recurrence": _cost_linear_recurrence, "gate_scan": _cost_rows(0), "post_norm": _cost_rows(0, 1),
     "relu_sq": _cost_rows(0), "scale_": _cost_rows(0), "scored_prepare": _cost_rows(0, 1, 2),
     "scored_prefill": _cost_scored_prefill, "scored_decode": _cost_scored_decode, "moe_route_top": _cost_rows(0),
