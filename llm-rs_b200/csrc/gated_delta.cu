@@ -16,8 +16,10 @@
 //   prepare      a block per token: convolutions + SiLU, unit q and k, g and beta, as float32 rows
 //   conv state   a block per request, after prepare: the request's last K - 1 convolution inputs
 //   recurrence   a block per (request, head, slice of 16 value columns) walks the request's tokens in order; four
-//                neighbouring lanes share a column, each with a quarter of the key channels in registers; k^T S and
-//                q^T S are summed over the four by two shuffles. Rows come in chunks through two shared-memory buffers.
+//                neighbouring lanes share a column, each with a quarter of the key channels in registers (lane p of the
+//                four holds channels 4 (p + 4 j) .. 4 (p + 4 j) + 3, so that the four read neighbouring 16-byte pieces
+//                of a row in shared memory, not pieces a bank's stride apart); k^T S and q^T S are summed over the four
+//                by two shuffles. Rows come in chunks through two shared-memory buffers.
 //   output       a warp per (token, head): norm, weight, gate
 #include "common.cuh"
 #include "mma_util.cuh"
@@ -76,29 +78,37 @@ __global__ void gdr_conv_state_kernel(const TA* __restrict__ x, long long stride
     }
 }
 
-constexpr int GD_COLS = 16, GD_LANES = 4, GD_THREADS = GD_COLS * GD_LANES;
+constexpr int GD_COLS = 16;      // value columns of a block
+#ifndef LLMRS_GD_LANES
+#define LLMRS_GD_LANES 8
+#endif
 
-template <int DMAX>
-__global__ void __launch_bounds__(GD_THREADS)
+// LANES: neighbouring lanes that share a column (4, 8 or 16; at most DMAX / 4, so that a lane holds whole pieces of
+// four channels).
+template <int DMAX, int LANES>
+__global__ void __launch_bounds__(GD_COLS * LANES)
 gdr_recurrence_kernel(const float* __restrict__ pq, const float* __restrict__ pk, const float* __restrict__ pv,
                       const float* __restrict__ pbeta, const float* __restrict__ pg, float* __restrict__ state,
                       const int* __restrict__ q_start, const int* __restrict__ n_new,
                       const int* __restrict__ slot_ids, float* __restrict__ o_raw, int G, int H, int d, int dv) {
   constexpr int CHUNK = DMAX >= 256 ? 8 : 16;
+  constexpr int GD_LANES = LANES, GD_THREADS = GD_COLS * LANES;
   constexpr int IPL = DMAX / GD_LANES;             // key channels per lane
   __shared__ __align__(16) float s_qk[2][2][CHUNK][DMAX];      // q, k of a chunk's tokens; channels >= d stay 0
   __shared__ float s_v[2][CHUNK][GD_COLS], s_bg[2][2][CHUNK];
   const int req = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * GD_COLS;
   const int kh = head / (H / G);
   const int tid = threadIdx.x;
-  const int col = col0 + tid / GD_LANES, part = tid % GD_LANES, i0 = part * IPL;
+  const int col = col0 + tid / GD_LANES, part = tid % GD_LANES;
+  // Register i of a lane holds key channel ch(i): pieces of four channels dealt out to the four lanes in turn.
+  auto ch = [&](int i) { return ((i >> 2) * GD_LANES + part) * 4 + (i & 3); };
   const bool live = col < dv;
   const int t0 = q_start[req], n = n_new[req];
   const int wq = G * d, wv = H * dv;
   float* S_g = state + ((size_t)slot_ids[req] * H + head) * d * dv;
   float S[IPL];
 #pragma unroll
-  for (int i = 0; i < IPL; ++i) S[i] = (live && i0 + i < d) ? S_g[(size_t)(i0 + i) * dv + col] : 0.f;
+  for (int i = 0; i < IPL; ++i) S[i] = (live && ch(i) < d) ? S_g[(size_t)ch(i) * dv + col] : 0.f;
   for (int e = tid; e < 2 * 2 * CHUNK * DMAX; e += GD_THREADS) (&s_qk[0][0][0][0])[e] = 0.f;
   for (int e = tid; e < 2 * CHUNK * GD_COLS; e += GD_THREADS) (&s_v[0][0][0])[e] = 0.f;
   __syncthreads();
@@ -146,7 +156,7 @@ gdr_recurrence_kernel(const float* __restrict__ pq, const float* __restrict__ pk
       float ks[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < IPL; i += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(&s_qk[buf][1][tt][i0 + i]);
+        const float4 k4 = *reinterpret_cast<const float4*>(&s_qk[buf][1][tt][ch(i)]);
         S[i] *= g; S[i + 1] *= g; S[i + 2] *= g; S[i + 3] *= g;
         ks[0] = fmaf(k4.x, S[i], ks[0]);
         ks[1] = fmaf(k4.y, S[i + 1], ks[1]);
@@ -154,14 +164,14 @@ gdr_recurrence_kernel(const float* __restrict__ pq, const float* __restrict__ pk
         ks[3] = fmaf(k4.w, S[i + 3], ks[3]);
       }
       float kS = (ks[0] + ks[1]) + (ks[2] + ks[3]);
-      kS += __shfl_xor_sync(0xffffffffu, kS, 1);
-      kS += __shfl_xor_sync(0xffffffffu, kS, 2);
+#pragma unroll
+      for (int off = 1; off < LANES; off <<= 1) kS += __shfl_xor_sync(0xffffffffu, kS, off);
       const float u = beta * (vj - kS);
       float os[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < IPL; i += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(&s_qk[buf][1][tt][i0 + i]);
-        const float4 q4 = *reinterpret_cast<const float4*>(&s_qk[buf][0][tt][i0 + i]);
+        const float4 k4 = *reinterpret_cast<const float4*>(&s_qk[buf][1][tt][ch(i)]);
+        const float4 q4 = *reinterpret_cast<const float4*>(&s_qk[buf][0][tt][ch(i)]);
         S[i] = fmaf(k4.x, u, S[i]);
         S[i + 1] = fmaf(k4.y, u, S[i + 1]);
         S[i + 2] = fmaf(k4.z, u, S[i + 2]);
@@ -172,8 +182,8 @@ gdr_recurrence_kernel(const float* __restrict__ pq, const float* __restrict__ pk
         os[3] = fmaf(S[i + 3], q4.w, os[3]);
       }
       float o = (os[0] + os[1]) + (os[2] + os[3]);
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
+#pragma unroll
+      for (int off = 1; off < LANES; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
       if (part == 0 && live) o_raw[(size_t)(t0 + c0 + tt) * wv + (size_t)head * dv + col] = o;
     }
     __syncthreads();
@@ -181,7 +191,7 @@ gdr_recurrence_kernel(const float* __restrict__ pq, const float* __restrict__ pk
   if (live) {
 #pragma unroll
     for (int i = 0; i < IPL; ++i)
-      if (i0 + i < d) S_g[(size_t)(i0 + i) * dv + col] = S[i];
+      if (ch(i) < d) S_g[(size_t)ch(i) * dv + col] = S[i];
   }
 }
 
@@ -238,6 +248,9 @@ LLMRS_API int llmrs_gated_delta(const void* x, long long x_stride, const void* g
   const int dmax = d <= 32 ? 32 : (d <= 64 ? 64 : (d <= 128 ? 128 : 256));
   dim3 grid(n_requests, H, (dv + GD_COLS - 1) / GD_COLS);
   const int rows = n_tokens * H;
+#define LLMRS_GD_REC(DMAX, LANES)                                                                                 \
+  gdr_recurrence_kernel<DMAX, LANES><<<grid, GD_COLS * LANES, 0, stream>>>(pq, pk, pv, pbeta, pg, state, q_start, n_new, \
+                                                                           slot_ids, o_raw, G, H, d, dv)
 #define LLMRS_GD_LAUNCH(T)                                                                                             \
   do {                                                                                                                 \
     static size_t configured = 48 * 1024;                                                                              \
@@ -257,10 +270,10 @@ LLMRS_API int llmrs_gated_delta(const void* x, long long x_stride, const void* g
       rc = llmrs_launch_status("gated_delta (convolution state)");                                                     \
       if (rc != 0) return rc;                                                                                          \
     }                                                                                                                  \
-    if (dmax == 32) gdr_recurrence_kernel<32><<<grid, GD_THREADS, 0, stream>>>(pq, pk, pv, pbeta, pg, state, q_start, n_new, slot_ids, o_raw, G, H, d, dv); \
-    else if (dmax == 64) gdr_recurrence_kernel<64><<<grid, GD_THREADS, 0, stream>>>(pq, pk, pv, pbeta, pg, state, q_start, n_new, slot_ids, o_raw, G, H, d, dv); \
-    else if (dmax == 128) gdr_recurrence_kernel<128><<<grid, GD_THREADS, 0, stream>>>(pq, pk, pv, pbeta, pg, state, q_start, n_new, slot_ids, o_raw, G, H, d, dv); \
-    else gdr_recurrence_kernel<256><<<grid, GD_THREADS, 0, stream>>>(pq, pk, pv, pbeta, pg, state, q_start, n_new, slot_ids, o_raw, G, H, d, dv); \
+    if (dmax == 32) LLMRS_GD_REC(32, (LLMRS_GD_LANES < 8 ? LLMRS_GD_LANES : 8));                                       \
+    else if (dmax == 64) LLMRS_GD_REC(64, LLMRS_GD_LANES);                                                             \
+    else if (dmax == 128) LLMRS_GD_REC(128, LLMRS_GD_LANES);                                                           \
+    else LLMRS_GD_REC(256, LLMRS_GD_LANES);                                                                            \
     rc = llmrs_launch_status("gated_delta (recurrence)");                                                              \
     if (rc != 0) return rc;                                                                                            \
     gdr_out_kernel<T><<<(rows + 3) / 4, 128, 0, stream>>>(o_raw, (const T*)gate, gate_stride, norm_w, (T*)out,         \
@@ -270,5 +283,6 @@ LLMRS_API int llmrs_gated_delta(const void* x, long long x_stride, const void* g
   else if (dtype == LLMRS_BF16) LLMRS_GD_LAUNCH(__nv_bfloat16);
   else return llmrs_fail("gated_delta: unknown dtype %d", dtype);
 #undef LLMRS_GD_LAUNCH
+#undef LLMRS_GD_REC
   return llmrs_launch_status("gated_delta (norm and gate)");
 }
