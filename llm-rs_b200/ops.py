@@ -1415,6 +1415,21 @@ def poly_norm(z: torch.Tensor, coeff: torch.Tensor, eps: float) -> torch.Tensor:
     return out
 
 
+GD_CHUNKED = os.environ.get("LLMRS_GD_CHUNKED", "0") == "1"
+_gd_chunked_set = None
+
+
+def gated_delta_chunked(on: bool) -> None:
+    """True: portions of 64 tokens and more take the gated delta rule in chunks of 32 tokens (five small float32 products
+    per chunk) instead of token by token; the same numbers up to rounding. Off unless ``LLMRS_GD_CHUNKED=1``: the
+    chunked kernel is bound by shared-memory reads and not ahead of the walk yet."""
+    global _gd_chunked_set
+    fn = _lib().llmrs_gated_delta_chunked
+    fn.restype, fn.argtypes = None, [ctypes.c_int]
+    fn(1 if on else 0)
+    _gd_chunked_set = bool(on)
+
+
 def gated_delta(x: torch.Tensor, gate: torch.Tensor, taps: torch.Tensor, ba: torch.Tensor, a_log: torch.Tensor,
                 dt_bias: torch.Tensor, norm_w: torch.Tensor, state: torch.Tensor, conv_state: torch.Tensor, ctx,
                 n_kv_heads: int, n_heads: int, dk: int, dv: int, key_eps: float, q_scale: float, norm_eps: float,
@@ -1426,6 +1441,8 @@ def gated_delta(x: torch.Tensor, gate: torch.Tensor, taps: torch.Tensor, ba: tor
     [tokens, heads * dv] in the activation type (``out``: a view to write into), multiplied by ``out_scale``."""
     C = 2 * n_kv_heads * dk + n_heads * dv
     K = taps.size(1)
+    if _gd_chunked_set is None:
+        gated_delta_chunked(GD_CHUNKED)
     _need(x, "x", contiguous=False)
     _need(gate, "gate", x.dtype, contiguous=False)
     for name, t in (("taps", taps), ("ba", ba), ("a_log", a_log), ("dt_bias", dt_bias), ("norm_w", norm_w),
@@ -1440,7 +1457,7 @@ def gated_delta(x: torch.Tensor, gate: torch.Tensor, taps: torch.Tensor, ba: tor
     if out is None:
         out = torch.empty((n, n_heads * dv), dtype=x.dtype, device=x.device)
     _need(out, "out", x.dtype, contiguous=False)
-    work = torch.empty((int(_lib_ll("llmrs_gated_delta_work_floats")(n, n_kv_heads, n_heads, dk, dv)),),
+    work = torch.empty((int(_lib_ll("llmrs_gated_delta_work_floats")(n, ctx.n_requests, n_kv_heads, n_heads, dk, dv)),),
                        dtype=torch.float32, device=x.device)
     _check(_lib().llmrs_gated_delta(
         _ptr(x), _LL(_row_stride(x, "x")), _ptr(gate), _LL(_row_stride(gate, "gate")), dtype_code(x.dtype), _ptr(taps),

@@ -442,6 +442,32 @@ def test_gated_delta_mixer_against_plain(dtype, heads, kv, dk, dv, conv, ):
         _close(got[r], want[r], dtype, r, f32=1e-4, bf16=0.04)
 
 
+@pytest.mark.parametrize("chunked", [True, False])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv,dk,dv,conv,lens,cuts", [
+    (4, 2, 16, 8, 4, (300, 77), [(64, 77), (100, 0), (136, 0)]),            # whole chunks, a ragged one, a short neighbour
+    (2, 1, 128, 32, 3, (257, 65), [(129, 1), (1, 64), (127, 0)]),           # one token beside a long portion
+    (3, 1, 12, 20, 2, (200, 200), [(33, 167), (167, 33)]),                  # value width no multiple of a slice
+    (1, 1, 200, 40, 4, (95, 96), [(95, 96)]),                               # keys of 200 channels
+    (4, 4, 32, 16, 5, (640, 3), [(639, 1), (1, 2)])])                       # twenty chunks in a row
+def test_long_portions_in_chunks_against_plain(dtype, heads, kv, dk, dv, conv, lens, cuts, chunked):
+    """Long portions token by token, and in chunks of 32 tokens (the form that ``LLMRS_GD_CHUNKED=1`` switches on for
+    portions of 64 tokens and more): the same numbers, from and into the same state, whatever the cut."""
+    from llm_rs_b200 import ops
+    part, w, state, m, g, D = _delta_setup(dtype, heads, kv, dk, dv, conv, dk + heads)
+    for t in state.values():
+        t[2:4].zero_()
+    seqs = [_rounded(torch.randn(n, D, generator=g), dtype) for n in lens]
+    want = [P.gated_delta(s.double(), m, _double(w), "m.", 1e-5) for s in seqs]
+    ops.gated_delta_chunked(chunked)
+    try:
+        got = _run_in_cuts(part, None, state, seqs, cuts, 16, dtype, g, 128)
+    finally:
+        ops.gated_delta_chunked(ops.GD_CHUNKED)
+    for r in range(2):
+        _close(got[r], want[r], dtype, r, f32=1e-4, bf16=0.04)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_the_recurrence_carries_its_state_over_a_long_decoding(dtype):
     """400 tokens one by one after a portion of two: the state and the convolution's rows travel through 400 steps; a
