@@ -71,8 +71,8 @@ FEKOLORN_C = {
     "architecture": "Fekolorn", "vocab": 512, "width": 256, "norm": {"eps": 1e-6}, "streams": 4,
     "embedding": {"scale": 1.5, "bigram": {"buckets": 1024, "mul_prev": 1, "mul_cur": 3}},
     "layers": _layers(
-        (_attention(8, 2, 64, 32, 0.125, window=48, bias=(16, 100), v_mix=True), _dense(256)),
-        (_parallel(_softmax(8, 2, 96, 32, 0.1, rot=(1e6, 32)), (4, 2, 64, 64, 4), 0.8, 0.9), _dense(128)),
+        (_attention(4, 2, 64, 32, 0.11, window=48, bias=(18, 100), v_mix=True), _dense(256)),
+        (_parallel(_softmax(6, 3, 96, 32, 0.1, rot=(1e6, 32)), (4, 2, 64, 64, 4), 0.75, 1.1), _dense(128)),
         (_attention(4, 2, 32, 32, 0.17, window=130, bias=(20, 130), v_mix=True), _dense(256)),
         (_parallel(_softmax(4, 4, 128, 128, 0.09, rot=(1e4, 128)), (2, 1, 128, 32, 3), 1.1, 0.7), _dense(64)))}
 

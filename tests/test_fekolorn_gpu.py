@@ -291,8 +291,8 @@ CUTS = [(97, 30), (2, 1), (1, 1), (30, 2), (1, 1), (19, 6), (0, 1), (1, 0)]     
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv,dk,dv,window,rot,bias,alone,page", [
     (4, 2, 16, 32, 20, 0, (8, 64), True, 16), (5, 1, 24, 8, 7, 0, (6, 5), True, 8), (2, 2, 8, 40, 1, 0, (2, 3), True, 4),
-    (6, 6, 64, 64, 96, 0, (16, 100), True, 16), (8, 2, 64, 32, 130, 0, (20, 130), True, 32), (3, 3, 128, 128, 0, 0, (32, 2000), True, 64),
-    (4, 4, 16, 16, 0, 8, None, False, 16), (8, 2, 96, 32, 0, 48, None, False, 16), (2, 1, 20, 12, 0, 4, None, False, 16),
+    (6, 6, 64, 64, 96, 0, (14, 100), True, 16), (8, 4, 64, 32, 130, 0, (20, 130), True, 32), (3, 3, 128, 128, 0, 0, (32, 2000), True, 64),
+    (4, 4, 16, 16, 0, 8, None, False, 16), (6, 3, 96, 32, 0, 64, None, False, 16), (2, 1, 20, 12, 0, 4, None, False, 16),
     (6, 1, 48, 32, 75, 48, (9, 40), False, 16), (7, 1, 40, 40, 0, 0, (3, 50), True, 16), (12, 3, 80, 48, 16, 80, None, False, 16),
     (4, 2, 128, 32, 0, 64, None, False, 16), (3, 1, 64, 16, 33, 0, (12, 33), True, 16)])
 def test_softmax_mixer_against_plain(dtype, heads, kv, dk, dv, window, rot, bias, alone, page, generic):
